@@ -26,6 +26,21 @@ SOURCES = [
     "attention.cu",
     "attention_prefill_tc.cu",
     "allreduce.cu",
+    "gemm_simt.cu",
+    "postnorm.cu",
+    "attention_sink.cu",
+    "mlstm.cu",
+]
+# What a layer-list decoder (attention with a softmax sink / matrix-memory recurrence, norm after the
+# sum) launches: a fresh checkout that only serves such a model compiles these and nothing else.
+LAYER_LIST_SOURCES = [
+    "runtime.cu",
+    "elementwise.cu",
+    "gemm_tcgen05.cu",
+    "gemm_simt.cu",
+    "postnorm.cu",
+    "attention_sink.cu",
+    "mlstm.cu",
 ]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -52,19 +67,37 @@ def _digest(paths) -> str:
     return h.hexdigest()
 
 
-def build(force: bool = False, verbose: bool = False, variant: str = "") -> Path:
+def _file_digest(src: Path, headers) -> str:
+    h = hashlib.sha256()
+    for p in [src, *headers]:
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def subset_lib(tag: str) -> Path:
+    return CSRC / f"libb200_{tag}.so"
+
+
+def build(force: bool = False, verbose: bool = False, variant: str = "", sources=None, tag: str = "") -> Path:
     """variant "" = the product library (dependents released after the kernel's own dependency wait);
-    "early" = libb200_early.so, the experimental build with the round-1 entry-time trigger
-    (-DB200_PDL_EARLY_TRIGGER), kept only to reproduce the hazard documented in DESIGN.md section 9."""
-    srcs = [CSRC / s for s in SOURCES]
-    deps = srcs + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + [
-        CSRC.parent.parent / "include" / "b200.h"
-    ]
-    lib = LIB if not variant else CSRC / f"libb200_{variant}.so"
+    "early" = libb200_early.so, the experimental build with the entry-time trigger
+    (-DB200_PDL_EARLY_TRIGGER), kept only to reproduce the hazard documented beside pdl_wait().
+    sources + tag: link only those files into libb200_<tag>.so (same ABI, fewer symbols) -- what a
+    process that serves one model family needs on a fresh checkout.  Objects are cached per source
+    file, so a later full build compiles only what is still missing."""
+    names = list(SOURCES if sources is None else sources)
+    srcs = [CSRC / s for s in names]
+    headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + [CSRC.parent.parent / "include" / "b200.h"]
+    if sources is not None and not tag:
+        raise ValueError("a subset build needs a tag")
+    lib = (LIB if not tag else subset_lib(tag)) if not variant else CSRC / f"libb200_{variant}.so"
     extra = {"": [], "early": ["-DB200_PDL_EARLY_TRIGGER=1"]}[variant]
     objdir = CSRC / ("build" if not variant else f"build_{variant}")
-    stamp = objdir / "stamp"
-    digest = _digest(deps) + variant
+    stamp = objdir / (f"stamp_{tag}" if tag else "stamp")
+    digests = {src: _file_digest(src, headers) + variant for src in srcs}
+    digest = hashlib.sha256("".join(f"{s.name}:{d};" for s, d in sorted(digests.items())).encode()).hexdigest()
     if not force and lib.exists() and stamp.exists() and stamp.read_text() == digest:
         return lib
     nvcc = _nvcc()
@@ -72,6 +105,9 @@ def build(force: bool = False, verbose: bool = False, variant: str = "") -> Path
 
     def compile_one(src: Path):
         obj = objdir / (src.stem + ".o")
+        mark = objdir / (src.stem + ".digest")
+        if not force and obj.exists() and mark.exists() and mark.read_text() == digests[src]:
+            return obj
         cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         log = objdir / (src.stem + ".log")
@@ -80,16 +116,30 @@ def build(force: bool = False, verbose: bool = False, variant: str = "") -> Path
             raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
         if verbose:
             sys.stderr.write(r.stderr)
+        mark.write_text(digests[src])
         return obj
 
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(compile_one, srcs))
-    cmd = [nvcc, "-shared", "-o", str(lib), *map(str, objs)]
+    tmp = lib.with_suffix(f".{os.getpid()}.tmp")
+    cmd = [nvcc, "-shared", "-o", str(tmp), *map(str, objs)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, lib)
     stamp.write_text(digest)
     return lib
+
+
+def is_current(lib: Path = LIB) -> bool:
+    """True when `lib` (the full library by default) exists and was built from the sources as they are."""
+    if lib != LIB or not lib.exists():
+        return False
+    headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + [CSRC.parent.parent / "include" / "b200.h"]
+    stamp = CSRC / "build" / "stamp"
+    digests = {CSRC / s: _file_digest(CSRC / s, headers) for s in SOURCES}
+    digest = hashlib.sha256("".join(f"{s.name}:{d};" for s, d in sorted(digests.items())).encode()).hexdigest()
+    return stamp.exists() and stamp.read_text() == digest
 
 
 if __name__ == "__main__":

@@ -70,6 +70,12 @@ def build_parser() -> argparse.ArgumentParser:
     est.add_argument("--gpu-memory-utilization", type=float, default=0.90)
     est.add_argument("--quantization", "-q", default=None, choices=[None, "fp8"])
     est.add_argument("--kv-tokens", type=int, default=None, help="KV-cache capacity to size the claim for")
+    rp = sub.add_parser("replay", help="replay a recorded schedule of token ids (JSON lines on stdin) and write logits")
+    rp.add_argument("--model", required=True, help="model directory (config.json + model.safetensors)")
+    rp.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    rp.add_argument("--out", required=True, help="directory for <step>.f32 logit files")
+    rp.add_argument("--max-tokens", type=int, required=True, help="tokens the KV pool holds (live requests, whole pages)")
+    rp.add_argument("--max-seqs", type=int, default=4, help="sequence / state slots")
     w = sub.add_parser("_worker", help=argparse.SUPPRESS)
     w.add_argument("--engine-json", required=True)
     return p
@@ -107,7 +113,8 @@ def _engine_config(args, tp: int):
                         max_num_batched_tokens=args.max_num_batched_tokens,
                         num_gpu_blocks=args.num_gpu_blocks_override, enforce_eager=args.enforce_eager,
                         enable_prefix_caching=args.enable_prefix_caching, quantization=args.quantization,
-                        mixed_steps=args.mixed_steps, seed=args.seed)
+                        mixed_steps=args.mixed_steps, seed=args.seed,
+                        dtype="float32" if getattr(args, "dtype", "") == "float32" else "bfloat16")
 
 
 def make_engine(ecfg):
@@ -157,6 +164,10 @@ def main(argv: Optional[List[str]] = None) -> int:
                             gpu_memory_utilization=args.gpu_memory_utilization, quantization=args.quantization)
         print(json.dumps(estimate(mcfg, ecfg, weights_on_disk=disk, kv_tokens=args.kv_tokens).to_dict(), indent=1))
         return 0
+    if args.cmd == "replay":
+        from .replay import run
+
+        return run(args.model, args.dtype, args.out, args.max_tokens, args.max_seqs)
     if args.cmd == "_worker":
         import json
 
@@ -169,8 +180,8 @@ def main(argv: Optional[List[str]] = None) -> int:
 
     if unknown:
         log.warning("ignoring unsupported engine flags: %s", " ".join(unknown))
-    if args.dtype not in ("auto", "bfloat16", "bf16"):
-        log.error("only bfloat16 is supported (got --dtype %s)", args.dtype)
+    if args.dtype not in ("auto", "bfloat16", "bf16", "float32"):
+        log.error("supported: bfloat16, float32 for the model families that have a 32-bit path (got --dtype %s)", args.dtype)
         return 2
     import torch
 

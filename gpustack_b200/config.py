@@ -14,6 +14,8 @@ from pathlib import Path
 from typing import Optional
 
 SUPPORTED_ARCHS = ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "MixtralForCausalLM")
+# designs whose config.json lists their layers one by one (LayerListConfig below)
+LAYER_LIST_ARCHS = ("Vodavik",)
 
 
 @dataclass
@@ -129,9 +131,14 @@ class ModelConfig:
             eos_token_ids=tuple(eos_all), rope_scaling=scaling)
 
     @staticmethod
-    def from_pretrained(model_path: str) -> "ModelConfig":
+    def from_pretrained(model_path: str):
+        """The model class is chosen by config.json: a Llama-class ModelConfig, or a LayerListConfig for
+        the designs in LAYER_LIST_ARCHS."""
         with open(Path(model_path) / "config.json") as f:
-            cfg = ModelConfig.from_dict(json.load(f))
+            d = json.load(f)
+        if architecture_of(d) in LAYER_LIST_ARCHS:
+            return LayerListConfig.from_dict(d)
+        cfg = ModelConfig.from_dict(d)
         # chat checkpoints list their turn terminators (<|eot_id|>, ...) in generation_config.json
         gen = Path(model_path) / "generation_config.json"
         if gen.exists():
@@ -192,6 +199,213 @@ class ModelConfig:
                              (self.eos_token_id if self.eos_token_id is not None else 2)),
             **({"rope_scaling": dict(self.rope_scaling)} if self.rope_scaling else {}),
         }
+
+
+def architecture_of(d: dict) -> str:
+    """`architectures: [name]` (HF) or `architecture: name`."""
+    if isinstance(d.get("architecture"), str):
+        return d["architecture"]
+    archs = d.get("architectures") or ["LlamaForCausalLM"]
+    return archs[0]
+
+
+# ------------------------------------------------------------------------------ layer-list designs
+@dataclass
+class AttentionSpec:
+    """Softmax attention mixer of a layer-list design.  Every option is a parameter, so another design can
+    combine them differently: separate key / value widths, per-head RMS norm of q and k, a query
+    temperature 1 + coef * ln(floor((p + 1) / every) + 1), a learned softmax sink, a sigmoid output
+    gate, q/k/v biases, keys and values taken from an earlier layer's cache (kv_from)."""
+    heads: int
+    kv_heads: int
+    dim: int                       # query / key width per head
+    vdim: int                      # value width per head
+    scale: float
+    qk_norm: bool = True
+    qkv_bias: bool = True
+    sink: bool = True
+    gate: bool = True
+    q_temp_coef: float = 0.0
+    q_temp_every: int = 0          # 0 = no temperature
+    kv_from: Optional[int] = None  # layer index whose cache this mixer reads
+
+    kind = "attention"
+
+    @property
+    def q_width(self) -> int:
+        return self.heads * self.dim
+
+    @property
+    def out_width(self) -> int:
+        return self.heads * self.vdim
+
+
+@dataclass
+class MLSTMSpec:
+    """Matrix-memory recurrent mixer (mLSTM): per-head state dim x vdim, gates capped by tanh."""
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+
+    kind = "mlstm"
+
+    @property
+    def out_width(self) -> int:
+        return self.heads * self.vdim
+
+
+@dataclass
+class MLPSpec:
+    kind: str                      # "dense": down(relu(up x)^2)
+    ff: int
+
+
+@dataclass
+class LayerSpec:
+    mixer: object                  # AttentionSpec | MLSTMSpec
+    mlp: Optional[MLPSpec]
+
+
+@dataclass
+class LayerListConfig:
+    """A decoder described layer by layer (config.json `layers`): each entry names its mixer, the mixer's
+    sizes and its feed-forward.  The residual stream is normalised AFTER each sum:
+    x <- LN(alpha * x + sublayer(x)), bias-free layer norm."""
+    architecture: str
+    vocab_size: int
+    hidden_size: int
+    layers: list
+    norm_eps: float = 1e-5
+    postln_alpha: float = 1.0
+    logit_scale: float = 1.0
+    max_position_embeddings: int = 1 << 20     # the design has no learned or tabulated positions
+    eos_token_id: Optional[int] = None
+    bos_token_id: Optional[int] = None
+    eos_token_ids: tuple = ()
+    # what the engine asks of any model config
+    quantization: Optional[str] = None
+    num_local_experts: int = 0
+    sliding_window: Optional[int] = None
+    tie_word_embeddings: bool = False
+
+    family = "layer_list"
+
+    @property
+    def num_hidden_layers(self) -> int:
+        return len(self.layers)
+
+    @property
+    def has_state(self) -> bool:
+        """True when some mixer carries a recurrent state per sequence (needs a state slot; no prefix reuse)."""
+        return any(l.mixer.kind == "mlstm" for l in self.layers)
+
+    def kv_owner(self, l: int) -> Optional[int]:
+        """Layer whose K/V cache layer l's attention reads (itself unless kv_from), None for other mixers."""
+        m = self.layers[l].mixer
+        if m.kind != "attention":
+            return None
+        return l if m.kv_from is None else int(m.kv_from)
+
+    def kv_bytes_per_token(self, tp: int = 1, elem_bytes: int = 2) -> int:
+        return sum(m.kv_heads * (m.dim + m.vdim) * elem_bytes for m in (l.mixer for l in self.layers)
+                   if m.kind == "attention" and m.kv_from is None)
+
+    def state_bytes_per_seq(self) -> int:
+        n = 0
+        for m in (l.mixer for l in self.layers):
+            if m.kind == "mlstm":
+                z = (m.vdim + 31) // 32
+                n += 4 * m.heads * (m.dim * m.vdim + z * m.dim + z)
+        return n
+
+    def weight_bytes(self, tp: int = 1, quantization: Optional[str] = None) -> int:
+        D, n = self.hidden_size, 0
+        for l in self.layers:
+            m = l.mixer
+            if m.kind == "attention":
+                kv = 0 if m.kv_from is not None else m.kv_heads * (m.dim + m.vdim)
+                n += D * (m.q_width + kv + (m.out_width if m.gate else 0)) + m.out_width * D
+            else:
+                n += D * (2 * m.heads * m.dim + 2 * m.out_width + 2 * m.heads) + m.out_width * D
+            if l.mlp is not None:
+                n += 2 * D * l.mlp.ff
+        return 2 * (n + self.vocab_size * D)
+
+    @staticmethod
+    def from_dict(d: dict) -> "LayerListConfig":
+        arch = architecture_of(d)
+        if arch not in LAYER_LIST_ARCHS:
+            raise ValueError(f"unsupported architecture {arch}; layer-list designs: {LAYER_LIST_ARCHS}")
+        layers = []
+        for i, e in enumerate(d["layers"]):
+            mx = e["mixer"]
+            if e["type"] == "attention":
+                qt = mx.get("q_temp") or {}
+                src = mx.get("kv_from")
+                spec = AttentionSpec(heads=int(mx["heads"]), kv_heads=int(mx.get("kv_heads", mx["heads"])),
+                                     dim=int(mx["dim"]), vdim=int(mx.get("vdim", mx["dim"])),
+                                     scale=float(mx["scale"]), q_temp_coef=float(qt.get("coef", 0.0)),
+                                     q_temp_every=int(qt.get("every", 0)), kv_from=None if src is None else int(src))
+                if spec.heads % spec.kv_heads:
+                    raise ValueError(f"layer {i}: heads {spec.heads} not a multiple of kv_heads {spec.kv_heads}")
+                if spec.kv_from is not None:
+                    if not (0 <= spec.kv_from < i) or d["layers"][spec.kv_from]["type"] != "attention" \
+                            or d["layers"][spec.kv_from]["mixer"].get("kv_from") is not None:
+                        raise ValueError(f"layer {i}: kv_from must name an earlier attention layer with its own cache")
+            elif e["type"] == "mlstm":
+                spec = MLSTMSpec(heads=int(mx["heads"]), dim=int(mx["dim"]), vdim=int(mx.get("vdim", mx["dim"])),
+                                 gate_cap=float(mx["gate_cap"]))
+            else:
+                raise ValueError(f"layer {i}: unknown mixer type {e['type']!r}")
+            mlp = e.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") != "dense":
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+                mlp = MLPSpec(kind="dense", ff=int(mlp["ff"]))
+            layers.append(LayerSpec(mixer=spec, mlp=mlp))
+        eos = d.get("eos_token_id")
+        eos_all = tuple(int(t) for t in eos) if isinstance(eos, list) else (() if eos is None else (int(eos),))
+        return LayerListConfig(architecture=arch, vocab_size=int(d["vocab"]), hidden_size=int(d["width"]), layers=layers,
+                               norm_eps=float(d["norm"]["eps"]), postln_alpha=float(d.get("postln_alpha", 1.0)),
+                               logit_scale=float(d.get("logit_scale", 1.0)), eos_token_ids=eos_all,
+                               eos_token_id=eos_all[0] if eos_all else None, bos_token_id=d.get("bos_token_id"))
+
+    def to_dict(self) -> dict:
+        """config.json of this model (the inverse of from_dict)."""
+        out = []
+        for l in self.layers:
+            m = l.mixer
+            if m.kind == "attention":
+                mx = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "scale": m.scale}
+                if m.q_temp_every:
+                    mx["q_temp"] = {"coef": m.q_temp_coef, "every": m.q_temp_every}
+                if m.kv_from is not None:
+                    mx["kv_from"] = m.kv_from
+            else:
+                mx = {"heads": m.heads, "dim": m.dim, "vdim": m.vdim, "gate_cap": m.gate_cap}
+            out.append({"type": m.kind, "mixer": mx,
+                        "mlp": None if l.mlp is None else {"kind": l.mlp.kind, "ff": l.mlp.ff}})
+        return {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size, "layers": out,
+                "norm": {"eps": self.norm_eps}, "postln_alpha": self.postln_alpha, "logit_scale": self.logit_scale}
+
+
+def vodavik_shape(width: int = 2048, layers: int = 4, heads: int = 16, kv_heads: int = 4, dim: int = 128,
+                  ff: int = 8192, vocab: int = 32000) -> LayerListConfig:
+    """A Vodavik model of real layer sizes for benchmarks (random weights): attention and mLSTM layers
+    alternate, every second attention layer reads the previous one's cache."""
+    specs = []
+    last_attn = None
+    for i in range(layers):
+        if i % 2 == 0:
+            share = last_attn if (last_attn is not None and (i // 2) % 2 == 1) else None
+            specs.append(LayerSpec(AttentionSpec(heads, kv_heads, dim, dim, dim ** -0.5, q_temp_coef=0.1, q_temp_every=1024,
+                                                 kv_from=share), MLPSpec("dense", ff)))
+            if share is None:
+                last_attn = i
+        else:
+            specs.append(LayerSpec(MLSTMSpec(max(1, heads // 2), dim, dim, 15.0), None))
+    return LayerListConfig("Vodavik", vocab, width, specs, norm_eps=1e-5, postln_alpha=2.0, logit_scale=1.0)
 
 
 # Named shapes used by tests and bench (random-init; there are no checkpoints offline).
@@ -260,6 +474,9 @@ class EngineConfig:
     # --speculative-config as a dict ({"method": "ngram", "num_speculative_tokens": k, ...}), None = off
     speculative_config: Optional[dict] = None
     seed: int = 0
+    dtype: str = "bfloat16"                   # "float32": activations, caches and every product in true 32-bit
+    #                                           (model families that have such a path; the others refuse it)
+    max_logit_rows: Optional[int] = None      # rows of one step whose logits can be kept (default: one per sequence)
     block_size: int = 16
     cuda_graph_sizes: list = field(default_factory=list)
 

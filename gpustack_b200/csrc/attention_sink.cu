@@ -1,0 +1,359 @@
+// Softmax attention over the paged KV cache for mixers whose key and value widths differ and are
+// not a tensor-core tile size, with the options such mixers combine:
+//   * per-head RMS norm of queries and keys (one weight vector of the head width, shared by heads),
+//   * no rotation; instead a query temperature  1 + c * ln(floor((p + 1) / n) + 1)  at position p,
+//   * a learned per-head SINK: exp(sink_h) is added to the softmax denominator (a virtual key whose
+//     score is sink_h, unscaled, and whose value is zero),
+//   * a sigmoid output gate read from the same fused projection as the queries,
+//   * keys / values that belong to an earlier layer's cache (the caller passes that cache).
+// Three kernels: `attn_prep` (bias + norms + temperature, in place for q, scatter of k and v into
+// the pages), `prefill` (a tile of 16 query rows of one sequence per CTA, keys staged in shared
+// memory 32 at a time, online softmax) and `decode` (one query row per CTA, the four warps walk
+// interleaved keys and merge).  Scores, softmax statistics and the accumulator are fp32; the element
+// type TA of the projection, the cache and the output is bf16, or fp32 for a model served in 32-bit.
+// Cache layout: K [blocks][G][page][dk], V [blocks][G][page][dv].
+#include "common.cuh"
+#include "runtime.h"
+#include "../../include/b200.h"
+
+#include <math_constants.h>
+
+namespace b200 {
+
+__device__ __forceinline__ float as_f32(float v) { return v; }
+__device__ __forceinline__ float as_f32(bf16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ void as_store(float* p, float v) { *p = v; }
+__device__ __forceinline__ void as_store(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+constexpr int kMaxDvPerLane = 8;   // value width <= 256
+
+// ----------------------------------------------------------------------------------------- prep
+// grid (T, H + 2G) (or (T, H) for a layer that reuses another layer's keys and values); one warp each.
+template <typename TA>
+__global__ void __launch_bounds__(32)
+attn_prep_kernel(TA* proj, int64_t ld, const bf16* __restrict__ bias, const bf16* __restrict__ qnorm_w,
+                 const bf16* __restrict__ knorm_w, const int32_t* __restrict__ positions,
+                 const int32_t* __restrict__ slots, TA* k_cache, TA* v_cache, int H, int G, int dk, int dv, int page,
+                 float eps, float temp_coef, int temp_every) {
+  const int t = blockIdx.x, hs = blockIdx.y, lane = threadIdx.x;
+  TA* row = proj + (size_t)t * ld;
+  if (hs < H + G) {
+    // a query head (hs < H) or a key head: bias, unit RMS over the head, weight, (temperature)
+    const bool is_q = hs < H;
+    const int col0 = hs * dk;                       // q heads then k heads are contiguous, both dk wide
+    const bf16* w = is_q ? qnorm_w : knorm_w;
+    float ss = 0.f;
+    for (int d = lane; d < dk; d += 32) {
+      float v = as_f32(row[col0 + d]);
+      if (bias != nullptr) v += __bfloat162float(bias[col0 + d]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    float mul = w != nullptr ? 1.0f / sqrtf(ss / (float)dk + eps) : 1.0f;   // no weight = no head norm
+    if (is_q && temp_every > 0) {
+      const int steps = (positions[t] + 1) / temp_every;
+      mul *= 1.0f + temp_coef * logf((float)steps + 1.0f);
+    }
+    TA* dst = row + col0;
+    if (!is_q) {
+      const int slot = slots[t];
+      if (slot < 0) return;
+      const int g = hs - H;
+      dst = k_cache + (((size_t)(slot / page) * G + g) * page + (slot % page)) * dk;
+    }
+    for (int d = lane; d < dk; d += 32) {
+      float v = as_f32(row[col0 + d]);
+      if (bias != nullptr) v += __bfloat162float(bias[col0 + d]);
+      const float wv = w != nullptr ? __bfloat162float(w[d]) : 1.0f;
+      as_store(dst + d, v * mul * wv);
+    }
+  } else {
+    const int g = hs - H - G;
+    const int col0 = (H + G) * dk + g * dv;
+    const int slot = slots[t];
+    if (slot < 0) return;
+    TA* dst = v_cache + (((size_t)(slot / page) * G + g) * page + (slot % page)) * dv;
+    for (int d = lane; d < dv; d += 32) {
+      float v = as_f32(row[col0 + d]);
+      if (bias != nullptr) v += __bfloat162float(bias[col0 + d]);
+      as_store(dst + d, v);
+    }
+  }
+}
+
+// -------------------------------------------------------------------------------------- prefill
+constexpr int kPfRows = 16, kPfKeys = 32, kPfWarps = 4, kPfRowsPerWarp = kPfRows / kPfWarps;
+
+// grid (tiles, H).  Tile i = rows [tile_q0[i], +16) of sequence tile_seq[i]; the sequence's new rows
+// are cu_q[s] .. cu_q[s+1]) of the projection and sit at positions ctx_lens[s] + row.
+template <typename TA>
+__global__ void __launch_bounds__(kPfWarps * 32)
+attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, const TA* __restrict__ k_cache,
+                         const TA* __restrict__ v_cache, const int32_t* __restrict__ block_table, int max_blocks,
+                         const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_lens,
+                         const int32_t* __restrict__ tile_seq, const int32_t* __restrict__ tile_q0,
+                         const float* __restrict__ sink, TA* out, int64_t ldo, int H, int G, int dk, int dv, int page,
+                         float scale) {
+  extern __shared__ float smem[];
+  float* Qs = smem;                                   // [16][dk]
+  float* Ks = Qs + kPfRows * dk;                      // [32][dk + 1]
+  float* Vs = Ks + kPfKeys * (dk + 1);                // [32][dv]
+  float* Ps = Vs + kPfKeys * dv;                      // [4 warps][4 rows][32]
+  const int tile = blockIdx.x, h = blockIdx.y, g = h / (H / G);
+  const int s = tile_seq[tile], q0 = tile_q0[tile];
+  const int row0 = cu_q[s], qlen = cu_q[s + 1] - row0, ctx = ctx_lens[s];
+  const int nrows = min(kPfRows, qlen - q0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int32_t* bt = block_table + (size_t)s * max_blocks;
+
+  for (int i = threadIdx.x; i < kPfRows * dk; i += blockDim.x) {
+    const int r = i / dk, d = i - r * dk;
+    Qs[i] = r < nrows ? as_f32(proj[(size_t)(row0 + q0 + r) * ld + h * dk + d]) : 0.f;
+  }
+  float m[kPfRowsPerWarp], l[kPfRowsPerWarp], acc[kPfRowsPerWarp][kMaxDvPerLane];
+#pragma unroll
+  for (int r = 0; r < kPfRowsPerWarp; ++r) {
+    // the sink opens the running softmax: a key with score sink_h and a zero value
+    m[r] = sink != nullptr ? sink[h] : -CUDART_INF_F;
+    l[r] = sink != nullptr ? 1.f : 0.f;
+#pragma unroll
+    for (int j = 0; j < kMaxDvPerLane; ++j) acc[r][j] = 0.f;
+  }
+  const int kv_end = ctx + q0 + nrows;                // keys this tile can see: [0, kv_end)
+  for (int k0 = 0; k0 < kv_end; k0 += kPfKeys) {
+    __syncthreads();                                  // previous block's K / V fully consumed (and Qs written)
+    // each warp stages 8 keys
+    for (int jj = 0; jj < kPfKeys / kPfWarps; ++jj) {
+      const int j = warp * (kPfKeys / kPfWarps) + jj;
+      const int key = k0 + j;
+      if (key < kv_end) {
+        const size_t base = ((size_t)bt[key / page] * G + g) * page + (key % page);
+        const TA* kp = k_cache + base * dk;
+        const TA* vp = v_cache + base * dv;
+        for (int d = lane; d < dk; d += 32) Ks[j * (dk + 1) + d] = as_f32(kp[d]);
+        for (int d = lane; d < dv; d += 32) Vs[j * dv + d] = as_f32(vp[d]);
+      } else {
+        for (int d = lane; d < dk; d += 32) Ks[j * (dk + 1) + d] = 0.f;
+        for (int d = lane; d < dv; d += 32) Vs[j * dv + d] = 0.f;
+      }
+    }
+    __syncthreads();
+    // scores of this warp's rows against key k0 + lane
+    float sc[kPfRowsPerWarp];
+#pragma unroll
+    for (int r = 0; r < kPfRowsPerWarp; ++r) sc[r] = 0.f;
+    const float* kr = Ks + lane * (dk + 1);
+    const float* qr = Qs + warp * kPfRowsPerWarp * dk;
+    for (int d = 0; d < dk; ++d) {
+      const float kv = kr[d];
+#pragma unroll
+      for (int r = 0; r < kPfRowsPerWarp; ++r) sc[r] = fmaf(qr[r * dk + d], kv, sc[r]);
+    }
+    float* pw = Ps + warp * kPfRowsPerWarp * 32;
+#pragma unroll
+    for (int r = 0; r < kPfRowsPerWarp; ++r) {
+      const int qpos = ctx + q0 + warp * kPfRowsPerWarp + r;
+      const bool seen = (k0 + lane) <= qpos && (k0 + lane) < kv_end;
+      const float sv = seen ? sc[r] * scale : -CUDART_INF_F;
+      const float mn = fmaxf(m[r], warp_max(sv));
+      float p = 0.f, corr = 1.f;
+      if (mn > -CUDART_INF_F) {
+        p = seen ? expf(sv - mn) : 0.f;
+        corr = expf(m[r] - mn);                       // m = -inf before the first key: exp(-inf) = 0
+      }
+      l[r] = l[r] * corr + warp_sum(p);
+      m[r] = mn;
+#pragma unroll
+      for (int j = 0; j < kMaxDvPerLane; ++j) acc[r][j] *= corr;
+      pw[r * 32 + lane] = p;
+    }
+    __syncwarp();
+    for (int j = 0; j < kPfKeys; ++j) {
+      float p[kPfRowsPerWarp];
+#pragma unroll
+      for (int r = 0; r < kPfRowsPerWarp; ++r) p[r] = pw[r * 32 + j];
+#pragma unroll
+      for (int c = 0; c < kMaxDvPerLane; ++c) {
+        const int d = lane + 32 * c;
+        if (d < dv) {
+          const float vv = Vs[j * dv + d];
+#pragma unroll
+          for (int r = 0; r < kPfRowsPerWarp; ++r) acc[r][c] = fmaf(p[r], vv, acc[r][c]);
+        }
+      }
+    }
+    __syncwarp();
+  }
+#pragma unroll
+  for (int r = 0; r < kPfRowsPerWarp; ++r) {
+    const int qr = warp * kPfRowsPerWarp + r;
+    if (qr >= nrows) continue;
+    const size_t t = (size_t)(row0 + q0 + qr);
+    const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
+#pragma unroll
+    for (int c = 0; c < kMaxDvPerLane; ++c) {
+      const int d = lane + 32 * c;
+      if (d < dv) {
+        float o = acc[r][c] * inv;
+        if (gate_col >= 0) {
+          const float gv = as_f32(proj[t * ld + gate_col + h * dv + d]);
+          o *= 1.0f / (1.0f + expf(-gv));
+        }
+        as_store(out + t * ldo + h * dv + d, o);
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------- decode
+constexpr int kDecWarps = 4;
+constexpr int kMaxDkPerLane = 8;   // key width <= 256
+
+// grid (B, H): sequence b's single new row is row b of proj / out; it sees keys [0, seq_lens[b]).
+template <typename TA>
+__global__ void __launch_bounds__(kDecWarps * 32)
+attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, const TA* __restrict__ k_cache,
+                        const TA* __restrict__ v_cache, const int32_t* __restrict__ block_table, int max_blocks,
+                        const int32_t* __restrict__ seq_lens, const float* __restrict__ sink, TA* out, int64_t ldo,
+                        int H, int G, int dk, int dv, int page, float scale) {
+  __shared__ float sm_m[kDecWarps], sm_l[kDecWarps];
+  extern __shared__ float sm_acc[];                   // [warps][dv]
+  const int b = blockIdx.x, h = blockIdx.y, g = h / (H / G);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = seq_lens[b];
+  const int32_t* bt = block_table + (size_t)b * max_blocks;
+  float q[kMaxDkPerLane];
+#pragma unroll
+  for (int c = 0; c < kMaxDkPerLane; ++c) {
+    const int d = lane + 32 * c;
+    q[c] = d < dk ? as_f32(proj[(size_t)b * ld + h * dk + d]) * scale : 0.f;
+  }
+  float m = -CUDART_INF_F, l = 0.f, acc[kMaxDvPerLane];
+  if (warp == 0 && sink != nullptr) { m = sink[h]; l = 1.f; }
+#pragma unroll
+  for (int c = 0; c < kMaxDvPerLane; ++c) acc[c] = 0.f;
+  for (int key = warp; key < n; key += kDecWarps) {
+    const size_t base = ((size_t)bt[key / page] * G + g) * page + (key % page);
+    const TA* kp = k_cache + base * dk;
+    const TA* vp = v_cache + base * dv;
+    float sdot = 0.f;
+#pragma unroll
+    for (int c = 0; c < kMaxDkPerLane; ++c) {
+      const int d = lane + 32 * c;
+      if (d < dk) sdot = fmaf(q[c], as_f32(kp[d]), sdot);
+    }
+    sdot = warp_sum(sdot);
+    const float mn = fmaxf(m, sdot);
+    const float corr = expf(m - mn), p = expf(sdot - mn);
+    l = l * corr + p;
+    m = mn;
+#pragma unroll
+    for (int c = 0; c < kMaxDvPerLane; ++c) {
+      const int d = lane + 32 * c;
+      if (d < dv) acc[c] = fmaf(p, as_f32(vp[d]), acc[c] * corr);
+    }
+  }
+  if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+  __syncthreads();
+  float mt = -CUDART_INF_F;
+#pragma unroll
+  for (int w = 0; w < kDecWarps; ++w) mt = fmaxf(mt, sm_m[w]);
+  const float mine = mt > -CUDART_INF_F && m > -CUDART_INF_F ? expf(m - mt) : 0.f;
+#pragma unroll
+  for (int c = 0; c < kMaxDvPerLane; ++c) {
+    const int d = lane + 32 * c;
+    if (d < dv) sm_acc[warp * dv + d] = acc[c] * mine;
+  }
+  __syncthreads();
+  float lt = 0.f;
+#pragma unroll
+  for (int w = 0; w < kDecWarps; ++w) lt += sm_m[w] > -CUDART_INF_F ? sm_l[w] * expf(sm_m[w] - mt) : 0.f;
+  const float inv = lt > 0.f ? 1.0f / lt : 0.f;
+  for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+    float o = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecWarps; ++w) o += sm_acc[w * dv + d];
+    o *= inv;
+    if (gate_col >= 0) {
+      const float gv = as_f32(proj[(size_t)b * ld + gate_col + h * dv + d]);
+      o *= 1.0f / (1.0f + expf(-gv));
+    }
+    as_store(out + (size_t)b * ldo + h * dv + d, o);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_attn_prep(void* proj, int f32, int64_t ld, const void* bias, const void* qnorm_w,
+                              const void* knorm_w, const int32_t* positions, const int32_t* slots, void* k_cache,
+                              void* v_cache, int T, int H, int G, int dk, int dv, int page, int has_kv, float eps,
+                              float temp_coef, int temp_every, void* stream) {
+  B200_REQUIRE(T >= 0 && H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && page > 0, "attn_prep: bad shape");
+  if (T == 0) return B200_OK;
+  dim3 grid(T, has_kv ? H + 2 * G : H);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (f32)
+    attn_prep_kernel<float><<<grid, 32, 0, s>>>((float*)proj, ld, (const bf16*)bias, (const bf16*)qnorm_w,
+                                                (const bf16*)knorm_w, positions, slots, (float*)k_cache,
+                                                (float*)v_cache, H, G, dk, dv, page, eps, temp_coef, temp_every);
+  else
+    attn_prep_kernel<bf16><<<grid, 32, 0, s>>>((bf16*)proj, ld, (const bf16*)bias, (const bf16*)qnorm_w,
+                                               (const bf16*)knorm_w, positions, slots, (bf16*)k_cache, (bf16*)v_cache,
+                                               H, G, dk, dv, page, eps, temp_coef, temp_every);
+  return b200_check_launch("b200_attn_prep");
+}
+
+extern "C" int b200_attn_sink_prefill_tile(void) { return kPfRows; }
+
+extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                      const void* v_cache, const int32_t* block_table, int max_blocks,
+                                      const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
+                                      const int32_t* tile_q0, int n_tiles, const float* sink, void* out, int64_t ldo,
+                                      int H, int G, int dk, int dv, int page, float scale, void* stream) {
+  B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 32 * kMaxDvPerLane && page > 0,
+               "attn_sink_prefill: bad shape H=%d G=%d dk=%d dv=%d", H, G, dk, dv);
+  if (n_tiles <= 0) return B200_OK;
+  const size_t smem = sizeof(float) * ((size_t)kPfRows * dk + (size_t)kPfKeys * (dk + 1) + (size_t)kPfKeys * dv +
+                                       (size_t)kPfWarps * kPfRowsPerWarp * 32);
+  B200_REQUIRE(smem <= 200 * 1024, "attn_sink_prefill: head widths %d / %d exceed shared memory", dk, dv);
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(n_tiles, H);
+  if (f32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(attn_sink_prefill_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attn_sink_prefill_kernel<float><<<grid, kPfWarps * 32, smem, s>>>(
+        (const float*)proj, ld, gate_col, (const float*)k_cache, (const float*)v_cache, block_table, max_blocks, cu_q,
+        ctx_lens, tile_seq, tile_q0, sink, (float*)out, ldo, H, G, dk, dv, page, scale);
+  } else {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(attn_sink_prefill_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attn_sink_prefill_kernel<bf16><<<grid, kPfWarps * 32, smem, s>>>(
+        (const bf16*)proj, ld, gate_col, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, cu_q,
+        ctx_lens, tile_seq, tile_q0, sink, (bf16*)out, ldo, H, G, dk, dv, page, scale);
+  }
+  return b200_check_launch("b200_attn_sink_prefill");
+}
+
+extern "C" int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                                     const void* v_cache, const int32_t* block_table, int max_blocks,
+                                     const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
+                                     int G, int dk, int dv, int page, float scale, void* stream) {
+  B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dk <= 32 * kMaxDkPerLane && dv > 0 &&
+                   dv <= 32 * kMaxDvPerLane && page > 0,
+               "attn_sink_decode: bad shape H=%d G=%d dk=%d dv=%d", H, G, dk, dv);
+  if (B <= 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t smem = sizeof(float) * kDecWarps * dv;
+  dim3 grid(B, H);
+  if (f32)
+    attn_sink_decode_kernel<float><<<grid, kDecWarps * 32, smem, s>>>(
+        (const float*)proj, ld, gate_col, (const float*)k_cache, (const float*)v_cache, block_table, max_blocks,
+        seq_lens, sink, (float*)out, ldo, H, G, dk, dv, page, scale);
+  else
+    attn_sink_decode_kernel<bf16><<<grid, kDecWarps * 32, smem, s>>>(
+        (const bf16*)proj, ld, gate_col, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, seq_lens,
+        sink, (bf16*)out, ldo, H, G, dk, dv, page, scale);
+  return b200_check_launch("b200_attn_sink_decode");
+}

@@ -18,11 +18,12 @@ import torch
 
 from .config import EngineConfig, ModelConfig
 from .lib import B200Error
+from .layer_list_runner import runner_class
 from .runner import ModelRunner
 from .scheduler import (DecodePlan, MixedPlan, PrefillPlan, Request, SamplingParams, Scheduler, SpecPlan, StepOutput,
                         kernel_temperature, step_seeds)
-from .weights import (ModelWeights, lazy_random_source, load_safetensors_dir, random_state_dict,
-                      shard_state_dict)
+from .weights import (ModelWeights, lazy_random_source, load_layer_list, load_layer_list_dir, load_safetensors_dir,
+                      random_layer_list_state, random_state_dict, shard_state_dict)
 
 log = logging.getLogger("b200.engine")
 
@@ -189,7 +190,7 @@ class LLMEngine:
             log.warning("sliding-window attention is not implemented: max_model_len capped at the window (%d)",
                         mcfg.sliding_window)
             ecfg.max_model_len = mcfg.sliding_window
-        self.runner = ModelRunner(mcfg, ecfg, weights, device=device, tp_group=tp.nccl if tp else None, tp_ctx=tp)
+        self.runner = runner_class(mcfg)(mcfg, ecfg, weights, device=device, tp_group=tp.nccl if tp else None, tp_ctx=tp)
         if tp and tp.shm is None:
             r = self.runner
             # largest payloads: decode = B*(2+max_blocks); prefill = 4*S + S*max_blocks + T
@@ -201,16 +202,23 @@ class LLMEngine:
             n = int(t[0])
         self.num_blocks = n
         self.runner.init_kv_cache(n)
+        # models with recurrent mixers: one state slot per sequence that can be admitted
+        self.state_slots = ecfg.max_num_seqs if getattr(mcfg, "has_state", False) else 0
+        if self.state_slots:
+            self.runner.init_state(self.state_slots)
         self.runner.capture_graphs()
         # extended KV cache: evicted prefix blocks go to pinned host memory (same slot count on every rank)
         host_slots = 0
         if ecfg.kv_host_cache_gib > 0 and ecfg.enable_prefix_caching:
             host_slots = int(ecfg.kv_host_cache_gib * (1 << 30)) // self.runner.kv_block_bytes()
         self.runner.init_host_kv(host_slots)
+        if self.state_slots:
+            host_slots = 0
         self.sched = Scheduler(n, ecfg.block_size, ecfg.max_num_seqs, ecfg.max_num_batched_tokens,
                                ecfg.max_model_len, mcfg.eos_token_ids or mcfg.eos_token_id, ecfg.enable_prefix_caching,
                                mixed_steps=ecfg.mixed_steps, speculative=ecfg.speculative(),
-                               max_sample_rows=self.runner.max_sample, kv_host_slots=host_slots)
+                               max_sample_rows=self.runner.max_sample, kv_host_slots=host_slots,
+                               state_slots=self.state_slots)
         self.requests: Dict[str, Request] = {}
         self.counters = {"prompt_tokens": 0, "generation_tokens": 0, "finished": 0, "steps": 0}
         self.step_time = {"prefill": 0.0, "decode": 0.0}
@@ -227,6 +235,15 @@ class LLMEngine:
                             "(launch one process per GPU, e.g. with torch.distributed.run)")
         rank = tp.rank if tp else 0
         device = f"cuda:{torch.cuda.current_device()}"
+        if state_dict is None and mcfg is None:
+            mcfg = ModelConfig.from_pretrained(ecfg.model)
+            if getattr(mcfg, "family", "") == "layer_list":
+                return cls(mcfg, ecfg, load_layer_list_dir(mcfg, ecfg.model, device), tp=tp, device=device)
+            mcfg = None
+        if mcfg is not None and getattr(mcfg, "family", "") == "layer_list":
+            if state_dict is None:
+                state_dict = random_layer_list_state(mcfg, seed=ecfg.seed, device=device)
+            return cls(mcfg, ecfg, load_layer_list(mcfg, lambda k: state_dict[k], device), tp=tp, device=device)
         if state_dict is None and mcfg is None:
             mcfg = ModelConfig.from_pretrained(ecfg.model)
             quant = ecfg.quantization or mcfg.quantization      # CLI flag, else the checkpoint's own config
@@ -293,7 +310,8 @@ class LLMEngine:
                                           s.block_table[:B].reshape(-1)])
                 self.tp.bcast_step([_KIND_DECODE, B], payload.astype(np.int32))
                 self.step_time["decode_bcast"] = self.step_time.get("decode_bcast", 0.0) + time.perf_counter() - tb
-            toks = self.runner.decode(B, s.last_token, s.num_computed, s.block_table, temps, seeds)
+            toks = self.runner.decode(B, s.last_token, s.num_computed, s.block_table, temps, seeds,
+                                      state_slots=s.state_slot if self.state_slots else None)
             toks = self._apply_sampling(list(s.rows[:B]), toks)
             out = s.update_decode(plan, toks)
             self.step_time["decode"] += time.perf_counter() - t0
@@ -311,7 +329,8 @@ class LLMEngine:
             sseeds = step_seeds(np.repeat(s.sample_seed[:B], counts), pos)
             if self.tp:
                 self._bcast_prefill(chunks, starts, tables, counts, None, stemps, sseeds)
-            toks = self.runner.prefill(chunks, starts, tables, counts, sample_temps=stemps, sample_seeds=sseeds)
+            toks = self.runner.prefill(chunks, starts, tables, counts, sample_temps=stemps, sample_seeds=sseeds,
+                                       state_slots=[int(x) for x in s.state_slot[:B]] if self.state_slots else None)
             # nucleus rows never carry drafts (one sampled row each): re-sampled on the host like in a decode step
             toks = self._apply_sampling([s.rows[i] for i in range(B) for _ in range(counts[i])], toks)
             out = s.update_spec(plan, toks)
@@ -331,8 +350,9 @@ class LLMEngine:
                                      step_seeds(s.sample_seed[:B], s.num_computed[:B])]).astype(np.uint32)
             if self.tp:
                 self._bcast_prefill(chunks, pre.starts, tables, pre.sample, dec, stemps, sseeds)
+            sslots = ([r.state_slot for r in pre.reqs] + [int(x) for x in s.state_slot[:B]]) if self.state_slots else None
             toks = self.runner.prefill(chunks, pre.starts, tables, pre.sample, decode=dec, sample_temps=stemps,
-                                       sample_seeds=sseeds)
+                                       sample_seeds=sseeds, state_slots=sslots)
             toks = self._apply_sampling(sampled + list(s.rows[:B]), toks)
             ns = len(sampled)
             if mixed:
@@ -347,6 +367,68 @@ class LLMEngine:
                 self.counters["finished"] += 1
                 self.requests.pop(rid, None)
         return out
+
+    # ------------------------------------------------------------------ replay of a given schedule
+    def replay_step(self, entries, end: Sequence[str] = ()) -> np.ndarray:
+        """Run ONE step whose batch is given instead of scheduled: entries = [(request id, next token ids,
+        wanted rows among them)].  A request is admitted at its first entry (state slot, then KV blocks as its
+        tokens arrive, from the scheduler's pools); it may skip steps; ids in `end` give everything back after the
+        step.  Entries that bring ONE token to a request with context run as decode rows -- a step of only
+        such rows is a decode step (CUDA-graph path), otherwise they ride in a mixed step beside the prompt
+        portions -- exactly the step functions generation uses.  Nothing is sampled into the requests: the
+        tokens are the caller's.  Returns the fp32 logits [wanted rows, vocab], entries in order."""
+        if self.tp is not None:
+            raise B200Error("replay_step runs on one GPU")
+        s = self.sched
+        chunks, singles = [], []          # (entry index, request, tokens, wanted rows)
+        for i, (rid, toks, want) in enumerate(entries):
+            toks = [int(t) for t in toks]
+            if not toks:
+                raise ValueError(f"request {rid}: an entry without tokens")
+            if any(t < 0 or t >= self.mcfg.vocab_size for t in toks):
+                raise ValueError("token id out of range")
+            r = self.requests.get(rid)
+            if r is None:
+                r = Request(req_id=rid, prompt_ids=[], params=SamplingParams(max_tokens=0))
+                s.replay_admit(r)
+                self.requests[rid] = r
+            s.replay_extend(r, len(toks))
+            want = sorted(int(x) for x in want)
+            (singles if (len(toks) == 1 and r.num_computed > 0) else chunks).append((i, r, toks, want))
+        B = len(singles)
+        mb = s.max_blocks_per_seq
+        last = np.asarray([e[2][0] for e in singles], dtype=np.int32)
+        comp = np.asarray([e[1].num_computed for e in singles], dtype=np.int32)
+        bt = np.zeros((max(B, 1), mb), dtype=np.int32)
+        for j, e in enumerate(singles):
+            bt[j, :len(e[1].blocks)] = e[1].blocks
+        dslots = np.asarray([e[1].state_slot for e in singles], dtype=np.int32)
+        if chunks:
+            self.runner.prefill([e[2] for e in chunks], [e[1].num_computed for e in chunks], [e[1].blocks for e in chunks],
+                                [e[3] for e in chunks], decode=(B, last, comp, bt) if B else None,
+                                state_slots=([e[1].state_slot for e in chunks] + dslots.tolist()) if self.state_slots else None)
+            n_chunk_rows = sum(len(e[3]) for e in chunks)
+            lg = self.runner.last_logits(n_chunk_rows + B)
+            parts, off = {}, 0
+            for e in chunks:
+                parts[e[0]] = lg[off:off + len(e[3])]
+                off += len(e[3])
+            for j, e in enumerate(singles):
+                parts[e[0]] = lg[n_chunk_rows + j:n_chunk_rows + j + 1] if e[3] else lg[:0]
+        else:
+            self.runner.decode(B, last, comp, bt, state_slots=dslots if self.state_slots else None)
+            lg = self.runner.last_logits(B)
+            parts = {e[0]: (lg[j:j + 1] if e[3] else lg[:0]) for j, e in enumerate(singles)}
+        for _, r, toks, _ in chunks + singles:
+            r.prompt_ids.extend(toks)
+            r.num_computed += len(toks)
+        for rid in end:
+            r = self.requests.pop(rid, None)
+            if r is not None:
+                s.replay_finish(r)
+        self.counters["steps"] += 1
+        out = [parts[i] for i in range(len(entries))]
+        return (torch.cat(out, dim=0) if out else self.runner.logits[:0]).float().cpu().numpy()
 
     def _apply_sampling(self, reqs, toks):
         """Plain temperature sampling happens in the sampler kernel (Gumbel-max, runner._sample); only

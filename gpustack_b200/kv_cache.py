@@ -217,6 +217,40 @@ class BlockPool:
         self._host.clear()
 
 
+class StateSlotPool:
+    """Slots for the per-sequence recurrent state of models with recurrent mixers (one slot holds the
+    state of EVERY recurrent layer for one sequence; the device tensors are the runner's).  A sequence
+    takes a slot at admission and gives it back when it finishes, is aborted or is preempted.  Slots are
+    handed out most-recently-freed first, so a freed slot is reused at once: the first step of the next
+    owner (context length 0) must not read what the slot holds -- the scan kernel starts from zero there."""
+
+    def __init__(self, num_slots: int):
+        if num_slots < 1:
+            raise ValueError("need at least one state slot")
+        self.num_slots = num_slots
+        self._free: List[int] = list(range(num_slots - 1, -1, -1))
+        self._used = [False] * num_slots
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def allocate(self) -> int:
+        if not self._free:
+            raise MemoryError("no free state slot")
+        s = self._free.pop()
+        self._used[s] = True
+        return s
+
+    def free(self, slot: int) -> None:
+        if slot < 0:
+            return
+        if not self._used[slot]:
+            raise ValueError(f"state slot {slot} is not in use")
+        self._used[slot] = False
+        self._free.append(slot)
+
+
 class SequenceBlocks:
     """Block table of one sequence."""
 

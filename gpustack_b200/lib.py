@@ -71,7 +71,32 @@ SIGNATURES = {
     "b200_tp_argmax_select": (_i32, [C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _i32, _i32, _i32, _vp, _i32, _vp]),
     "b200_allreduce_rs_norm_ag": (_i32, [C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _i32, _i32, _vp, _vp, _vp,
                                          _i32, _i32, _f32, _vp]),
+    "b200_linear_simt": (_i32, [_vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _vp]),
+    "b200_sum_layer_norm": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _f32, _f32, _vp]),
+    "b200_embed_rows_f32": (_i32, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "b200_relu2": (_i32, [_vp, _vp, _i32, _i64, _vp]),
+    "b200_attn_prep": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32,
+                              _i32, _f32, _f32, _i32, _vp]),
+    "b200_attn_sink_prefill_tile": (_i32, []),
+    "b200_attn_sink_prefill": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp,
+                                      _i64, _i32, _i32, _i32, _i32, _i32, _f32, _vp]),
+    "b200_attn_sink_decode": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _i64, _i32, _i32,
+                                     _i32, _i32, _i32, _f32, _vp]),
+    "b200_mlstm_state_slices": (_i32, [_i32]),
+    "b200_mlstm_scan": (_i32, [_vp, _i32, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
+                               _i32, _i32, _f32, _f32, _vp]),
+    "b200_mlstm_out": (_i32, [_vp, _vp, _i32, _i64, _i32, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _vp]),
 }
+
+# A process that serves ONE model family may ask for a library linked from that family's sources only
+# (build.LAYER_LIST_SOURCES, ...): prefer_subset(tag, sources) before the first load().  The full
+# library is used whenever it is already built and current.
+_SUBSET = None
+
+
+def prefer_subset(tag: str, sources) -> None:
+    global _SUBSET
+    _SUBSET = (tag, list(sources))
 
 
 def lib_path() -> Path:
@@ -87,15 +112,26 @@ def load(build_if_missing: bool = True):
         if _LIB is not None:
             return _LIB
         path = lib_path()
-        if not path.exists():
+        partial = False
+        if os.environ.get("B200_LIB"):
+            if not path.exists():
+                raise B200Error(f"{path} is missing")
+        elif _SUBSET is not None and not _build.is_current():
             if not build_if_missing:
                 raise B200Error(f"{path} is missing; run `python -m gpustack_b200.build`")
-            _build.build()
+            path = _build.build(sources=_SUBSET[1], tag=_SUBSET[0])
+            partial = True
+        elif build_if_missing:
+            _build.build()          # a no-op when the library is current; objects are cached per source
+        elif not path.exists():
+            raise B200Error(f"{path} is missing; run `python -m gpustack_b200.build`")
         lib = C.CDLL(str(path))
         for name, (res, args) in SIGNATURES.items():
             try:
                 fn = getattr(lib, name)
-            except AttributeError as e:  # pragma: no cover - a stale .so
+            except AttributeError as e:
+                if partial:         # not part of this family's sources: calling it raises AttributeError
+                    continue
                 raise B200Error(f"{path} does not export {name}; rebuild it") from e
             fn.restype = res
             fn.argtypes = args

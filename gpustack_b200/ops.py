@@ -405,3 +405,126 @@ def paged_attn_prefill(q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_len
                                          _p(tile_q0), tile_seq.shape[0], _p(out), Hq, Hkv, D,
                                          k_cache.shape[2], scale, _stream()), "paged_attn_prefill")
     return out
+
+
+# ----------------------------------------------------------- layer-list decoders (fp32 residual stream)
+def _is_f32(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 1
+    if t.dtype == torch.bfloat16:
+        return 0
+    raise B200Error(f"expected bf16 or fp32, got {t.dtype}")
+
+
+def _cuda(*ts) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise B200Error("expected CUDA tensors (there is no CPU path)")
+
+
+def linear(x, w, out, bias=None):
+    """out = x @ w.T (+ bias).  bf16 x / bf16 or fp32 out with K a multiple of 64 and 16-byte aligned rows
+    go to the tcgen05 GEMM; every other case (fp32 activations = a model served in true 32-bit; odd
+    shapes) runs on the CUDA cores with fp32 FMA accumulation."""
+    _cuda(x, w, out, bias)
+    if w.dtype != torch.bfloat16 or x.stride(-1) != 1 or w.stride(-1) != 1 or out.stride(-1) != 1:
+        raise B200Error("linear: bf16 weights and contiguous rows required")
+    M, K = x.shape
+    N = w.shape[0]
+    xf, yf = _is_f32(x), _is_f32(out)
+    if (not xf and bias is None and K % 64 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and (out.stride(0) * out.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
+        return gemm(x, w, out=out, out_dtype=out.dtype)
+    check(load().b200_linear_simt(_p(x), xf, _p(w), _p(bias), _p(out), yf, M, N, K, x.stride(0), w.stride(0),
+                                  out.stride(0), _stream()), "linear_simt")
+    return out
+
+
+def sum_layer_norm(y, x_in, w, alpha: float, eps: float, x_out=None, xb_out=None, rows=None, out_scale: float = 1.0):
+    """o = LN(alpha * x_in + y) * w * out_scale (y None: LN(x_in); rows: gather x_in[rows]); fp32 statistics.
+    x_out (fp32 residual stream) and / or xb_out (next projection's input, bf16 or fp32) receive o."""
+    _cuda(y, x_in, w, x_out, xb_out, rows)
+    if x_in.dtype != torch.float32 or (x_out is not None and x_out.dtype != torch.float32):
+        raise B200Error("sum_layer_norm: the residual stream is fp32")
+    D = x_in.shape[1]
+    T = (rows.shape[0] if rows is not None else x_in.shape[0]) if y is None else y.shape[0]
+    check(load().b200_sum_layer_norm(_p(y), 0 if y is None else _is_f32(y), 0 if y is None else y.stride(0), _p(x_in),
+                                     _p(rows), _p(w), _p(x_out), _p(xb_out), 0 if xb_out is None else _is_f32(xb_out),
+                                     T, D, alpha, eps, out_scale, _stream()), "sum_layer_norm")
+
+
+def embed_rows(ids, table, x_out, xb_out=None):
+    _cuda(ids, table, x_out, xb_out)
+    _req(ids, torch.int32, "ids"); _req(table, torch.bfloat16, "table"); _req(x_out, torch.float32, "x_out")
+    check(load().b200_embed_rows_f32(_p(ids), _p(table), _p(x_out), _p(xb_out), 0 if xb_out is None else _is_f32(xb_out),
+                                     ids.shape[0], table.shape[1], table.shape[0], _stream()), "embed_rows")
+
+
+def relu2(u, out=None):
+    _cuda(u, out)
+    out = u if out is None else out
+    if not u.is_contiguous() or not out.is_contiguous():
+        raise B200Error("relu2: contiguous tensors required")
+    check(load().b200_relu2(_p(u), _p(out), _is_f32(u), u.numel(), _stream()), "relu2")
+    return out
+
+
+def attn_prep(proj, bias, q_norm, k_norm, positions, slots, k_cache, v_cache, H, G, dk, dv, eps,
+              temp_coef: float = 0.0, temp_every: int = 0):
+    """In place on the fused projection rows: bias, per-head RMS norm of q and k, query temperature; k and v
+    go to their pages (k_cache None: a mixer that reads another layer's cache)."""
+    _cuda(proj, bias, q_norm, k_norm, positions, slots, k_cache, v_cache)
+    has_kv = k_cache is not None
+    page = k_cache.shape[2] if has_kv else 1
+    check(load().b200_attn_prep(_p(proj), _is_f32(proj), proj.stride(0), _p(bias), _p(q_norm), _p(k_norm), _p(positions),
+                                _p(slots), _p(k_cache), _p(v_cache), proj.shape[0], H, G, dk, dv, page, 1 if has_kv else 0,
+                                eps, temp_coef, temp_every, _stream()), "attn_prep")
+
+
+def attn_sink_prefill_tile() -> int:
+    return load().b200_attn_sink_prefill_tile()
+
+
+def attn_sink_prefill(proj, gate_col, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out,
+                      H, G, dk, dv, scale):
+    _cuda(proj, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out)
+    if k_cache.dtype != proj.dtype or out.dtype != proj.dtype:
+        raise B200Error("attn_sink_prefill: projection, cache and output must share one element type")
+    check(load().b200_attn_sink_prefill(_p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(k_cache), _p(v_cache),
+                                        _p(block_table), block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq),
+                                        _p(tile_q0), tile_seq.shape[0], _p(sink), _p(out), out.stride(0), H, G, dk, dv,
+                                        k_cache.shape[2], scale, _stream()), "attn_sink_prefill")
+    return out
+
+
+def attn_sink_decode(proj, gate_col, k_cache, v_cache, block_table, seq_lens, sink, out, H, G, dk, dv, scale):
+    _cuda(proj, k_cache, v_cache, block_table, seq_lens, sink, out)
+    if k_cache.dtype != proj.dtype or out.dtype != proj.dtype:
+        raise B200Error("attn_sink_decode: projection, cache and output must share one element type")
+    check(load().b200_attn_sink_decode(_p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(k_cache), _p(v_cache),
+                                       _p(block_table), block_table.shape[1], _p(seq_lens), seq_lens.shape[0], _p(sink),
+                                       _p(out), out.stride(0), H, G, dk, dv, k_cache.shape[2], scale, _stream()),
+          "attn_sink_decode")
+    return out
+
+
+def mlstm_state_slices(dv: int) -> int:
+    return (dv + 31) // 32
+
+
+def mlstm_scan(proj, q_col, k_col, v_col, gates, gate_bias, cu_seq, ctx_lens, state_slots, S, n, m, o_raw, H, dk, dv,
+               cap: float):
+    """Runs every sequence's new rows through the matrix-memory recurrence (state slot in, state slot out)."""
+    _cuda(proj, gates, gate_bias, cu_seq, ctx_lens, state_slots, S, n, m, o_raw)
+    _req(gates, torch.float32, "gates"); _req(S, torch.float32, "S"); _req(o_raw, torch.float32, "o_raw")
+    check(load().b200_mlstm_scan(_p(proj), _is_f32(proj), proj.stride(0), q_col, k_col, v_col, _p(gates), _p(gate_bias),
+                                 _p(cu_seq), _p(ctx_lens), _p(state_slots), _p(S), _p(n), _p(m), _p(o_raw),
+                                 state_slots.shape[0], H, dk, dv, cap, dk ** -0.5, _stream()), "mlstm_scan")
+
+
+def mlstm_out(o_raw, proj, gate_col, norm_w, out, H, dv, eps):
+    _cuda(o_raw, proj, norm_w, out)
+    check(load().b200_mlstm_out(_p(o_raw), _p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(norm_w), _p(out),
+                                out.stride(0), o_raw.shape[0], H, dv, eps, _stream()), "mlstm_out")
+    return out

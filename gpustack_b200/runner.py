@@ -36,21 +36,22 @@ def _align(n: int, a: int = 4) -> int:
 
 
 class ModelRunner:
+    SUPPORTS_FP32 = False
+
     def __init__(self, mcfg: ModelConfig, ecfg: EngineConfig, weights: ModelWeights, device: str = "cuda",
                  tp_group=None, tp_ctx=None):
         if not torch.cuda.is_available():
             raise B200Error("ModelRunner needs a CUDA device: this engine has no CPU path")
+        if ecfg.dtype not in ("bfloat16", "float32"):
+            raise B200Error(f"unknown dtype {ecfg.dtype!r} (bfloat16 | float32)")
+        if ecfg.dtype == "float32" and not self.SUPPORTS_FP32:
+            raise B200Error(f"{type(self).__name__} has no 32-bit path: serve this model with dtype=bfloat16")
         self.mcfg, self.ecfg, self.w = mcfg, ecfg, weights
         self.device = torch.device(device)
         self.tp = ecfg.tensor_parallel_size
         self.tp_group = tp_group
-        self.Hq = mcfg.num_attention_heads // self.tp
-        self.Hkv = mcfg.num_key_value_heads // self.tp
-        self.D = mcfg.head_dim
         self.H = mcfg.hidden_size
-        self.I = mcfg.intermediate_size // self.tp
-        self.qkv_width = (self.Hq + 2 * self.Hkv) * self.D
-        self.scale = self.D ** -0.5
+        self._init_model_dims()
         self.max_model_len = ecfg.max_model_len or mcfg.max_position_embeddings
         self.block_size = ecfg.block_size
         self.max_blocks = (self.max_model_len + self.block_size - 1) // self.block_size
@@ -59,9 +60,9 @@ class ModelRunner:
         # rows one step may sample: one per sequence, (1 + k) per sequence when speculative decoding
         # verifies k drafts per step (spec_decode.py)
         self.max_sample = min(self.max_tokens, self.max_seqs * (1 + ecfg.num_speculative_tokens))
-        self.prefill_tile = ops.attn_prefill_tile(self.Hq, self.Hkv)
+        if ecfg.max_logit_rows:      # a step may be asked for the logits of more rows than it has sequences
+            self.max_sample = min(self.max_tokens, max(self.max_sample, int(ecfg.max_logit_rows)))
         self.v_local = weights.lm_head.shape[0]
-        self.fp8 = weights.layers[0].qkv.dtype == ops.FP8
         self._alloc_workspace()
         self.k_cache: List[torch.Tensor] = []
         self.v_cache: List[torch.Tensor] = []
@@ -95,7 +96,23 @@ class ModelRunner:
         self.launches_per_decode = 0
 
     # ------------------------------------------------------------------------------ memory
+    def _init_model_dims(self):
+        """Sizes of the model family this runner executes (a Llama-class decoder here)."""
+        mcfg, weights = self.mcfg, self.w
+        self.Hq = mcfg.num_attention_heads // self.tp
+        self.Hkv = mcfg.num_key_value_heads // self.tp
+        self.D = mcfg.head_dim
+        self.I = mcfg.intermediate_size // self.tp
+        self.qkv_width = (self.Hq + 2 * self.Hkv) * self.D
+        self.scale = self.D ** -0.5
+        self.prefill_tile = ops.attn_prefill_tile(self.Hq, self.Hkv)
+        self.fp8 = weights.layers[0].qkv.dtype == ops.FP8
+
     def _alloc_workspace(self):
+        self._alloc_model_buffers()
+        self._alloc_step_io()
+
+    def _alloc_model_buffers(self):
         dev, T, H = self.device, self.max_tokens, self.H
         e = lambda *s, dt=BF16: torch.empty(*s, dtype=dt, device=dev)
         self.resid = e(T, H)
@@ -111,17 +128,22 @@ class ModelRunner:
             kmax = max(H, self.Hq * self.D, self.I)
             self.xq = e(T * kmax, dt=ops.FP8)          # flat; viewed [T, K] per projection
             self.xs = e(T, dt=torch.float32)
-        self.x_last = e(self.max_sample, H)
-        self.logits = e(self.max_sample, self.v_local, dt=torch.float32)
-        self.out_ids = torch.zeros(self.max_sample, dtype=torch.int32, device=dev)
-        self.out_vals = torch.zeros(self.max_sample, dtype=torch.float32, device=dev)
         has_bias = self.w.layers[0].qkv_bias is not None
         n_part = max(8 * min(_SPLITK_MAX_M, T) * max(H, self.qkv_width), T * self.qkv_width if has_bias else 0)
         self.partials = e(n_part, dt=torch.float32)   # flat: [splits, T, W]
         self.cos_sin = self._cos_sin_cache().to(dev)
-        # one int32 staging area for all step inputs (host pinned + device mirror)
+
+    def _alloc_step_io(self):
+        """Buffers every model family shares: sampled rows, logits, and ONE int32 staging area for all
+        step inputs (host pinned + device mirror)."""
+        dev, T, H = self.device, self.max_tokens, self.H
+        e = lambda *s, dt=BF16: torch.empty(*s, dtype=dt, device=dev)
+        self.x_last = e(self.max_sample, H)
+        self.logits = e(self.max_sample, self.v_local, dt=torch.float32)
+        self.out_ids = torch.zeros(self.max_sample, dtype=torch.int32, device=dev)
+        self.out_vals = torch.zeros(self.max_sample, dtype=torch.float32, device=dev)
         n_tiles_max = T // self.prefill_tile + self.max_seqs + 1
-        self.stage_words = 3 * _align(T) + 6 * _align(self.max_seqs + 1) + 3 * _align(self.max_sample + 1) \
+        self.stage_words = 3 * _align(T) + 10 * _align(self.max_seqs + 1) + 3 * _align(self.max_sample + 1) \
             + 2 * _align(n_tiles_max) + self.max_seqs * self.max_blocks + 64
         self.stage_host = torch.zeros(self.stage_words, dtype=torch.int32, pin_memory=True)
         self.stage_np = self.stage_host.numpy()
@@ -131,8 +153,10 @@ class ModelRunner:
         S = self.max_seqs
         self.d_ids, self.d_pos, self.d_slots, self.d_lens = 0, S, 2 * S, 3 * S
         self.d_temp, self.d_seed = 4 * S, 5 * S          # in-kernel sampler: fp32 temperatures (bit patterns), uint32 seeds
-        self.d_bt = 6 * S
+        self.d_state = 6 * S                             # recurrent-state slot of each row (-1 = none)
+        self.d_bt = 7 * S
         self._attn_ws: Optional[torch.Tensor] = None
+        self.arange_dev = torch.arange(self.max_seqs + 1, dtype=torch.int32, device=dev)
 
     def _cos_sin_cache(self) -> torch.Tensor:
         # $VLLM/model_executor/layers/rotary_embedding/base.py:71-93; kept in the model dtype
@@ -435,6 +459,11 @@ class ModelRunner:
         self._slots = sd[self.d_slots:self.d_slots + B]
         lens = sd[self.d_lens:self.d_lens + B]
         bt = sd[self.d_bt:self.d_bt + B * self.max_blocks].view(B, self.max_blocks)
+        self._forward_decode(ids, B, bt, lens, sd[self.d_state:self.d_state + B])
+        self._sample(B, None, sd[self.d_temp:self.d_temp + B].view(torch.float32), sd[self.d_seed:self.d_seed + B])
+
+    def _forward_decode(self, ids, B: int, bt, lens, state_slots) -> None:
+        """Embedding + all layers of a pure decode step (one new row per sequence) -> self.xn[:B]."""
         self._embed(ids, B)
         splits, ws = self._decode_attn_plan(B)
 
@@ -444,12 +473,17 @@ class ModelRunner:
                                   num_splits=splits, workspace=ws)
 
         self._layers(B, attn)
-        self._sample(B, None, sd[self.d_temp:self.d_temp + B].view(torch.float32), sd[self.d_seed:self.d_seed + B])
+
+    def _prepare_capture(self) -> None:
+        """Step inputs the warm-up and capture launches run on: token 0 at position 0, zero-length
+        attention, cache writes into the null block, no recurrent-state slot."""
+        self.stage_dev.zero_()
+        self.stage_dev[self.d_state:self.d_state + self.max_seqs] = -1
 
     def capture_graphs(self) -> None:
         if self.ecfg.enforce_eager:
             return
-        self.stage_dev.zero_()
+        self._prepare_capture()
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
@@ -470,7 +504,8 @@ class ModelRunner:
         self.stats["kernel_launches"] = 0
 
     def decode(self, B: int, last_token: np.ndarray, num_computed: np.ndarray, block_table: np.ndarray,
-               temps: Optional[np.ndarray] = None, seeds: Optional[np.ndarray] = None) -> np.ndarray:
+               temps: Optional[np.ndarray] = None, seeds: Optional[np.ndarray] = None,
+               state_slots: Optional[np.ndarray] = None) -> np.ndarray:
         """One decode step for rows 0..B-1 of the scheduler's persistent batch.  temps (fp32) / seeds
         (uint32, already mixed with the position) per row drive the in-kernel sampler; None = greedy."""
         S, bs = self.max_seqs, self.block_size
@@ -491,7 +526,10 @@ class ModelRunner:
             st[self.d_temp:self.d_temp + B] = np.asarray(temps[:B], dtype=np.float32).view(np.int32)
             st[self.d_seed:self.d_seed + B] = np.asarray(seeds[:B], dtype=np.uint32).view(np.int32)
             st[self.d_temp + B:self.d_temp + Bp] = 0
-        if Bp > B:   # padding rows: no cache write, zero-length attention
+        st[self.d_state:self.d_state + Bp] = -1
+        if state_slots is not None:
+            st[self.d_state:self.d_state + B] = state_slots[:B]
+        if Bp > B:   # padding rows: no cache write, zero-length attention, no state
             st[self.d_ids + B:self.d_ids + Bp] = 0
             st[self.d_pos + B:self.d_pos + Bp] = 0
             st[self.d_slots + B:self.d_slots + Bp] = -1
@@ -518,7 +556,7 @@ class ModelRunner:
     # ------------------------------------------------------------------------------ prefill
     def prefill(self, token_chunks: Sequence[Sequence[int]], starts: Sequence[int], block_tables: Sequence[Sequence[int]],
                 sample: Sequence[bool], decode=None, sample_temps: Optional[Sequence[float]] = None,
-                sample_seeds: Optional[Sequence[int]] = None) -> np.ndarray:
+                sample_seeds: Optional[Sequence[int]] = None, state_slots: Optional[Sequence[int]] = None) -> np.ndarray:
         """Runs one (chunked) prefill step.  token_chunks[s] are the ids of chunk s, which occupies
         positions [starts[s], starts[s]+len).  sample[s] is the number of TRAILING rows of chunk s whose
         next token is sampled (False/0: none, True/1: the last row = a completed prompt, 1 + k: every row
@@ -526,7 +564,10 @@ class ModelRunner:
         decode = (B, last_token, num_computed, block_table) makes it a MIXED step: rows 0..B-1 of the
         scheduler's persistent batch ride along with one decode token each (appended after the
         prefill tokens: same GEMMs / norms / RoPE launches, the weights are streamed once for
-        both); their B tokens follow the prefill tokens in the returned array."""
+        both); their B tokens follow the prefill tokens in the returned array.
+        sample[s] may also be a LIST of row offsets inside chunk s (a replayed step asks for the logits of
+        chosen rows).  state_slots: recurrent-state slot of every chunk, then of every riding decode row
+        (models with recurrent mixers; None = no state)."""
         S = len(token_chunks)
         lens = [len(c) for c in token_chunks]
         Tp = sum(lens)
@@ -537,8 +578,11 @@ class ModelRunner:
         bs = self.block_size
         st = self.stage_np
         o_ids, o_pos, o_slots = 0, _align(T), 2 * _align(T)
-        counts = [min(int(c), n) for c, n in zip(sample, lens)]     # bool -> 0 / 1
-        NS = sum(counts) + Bd
+        picks = [sorted(int(x) for x in c) if isinstance(c, (list, tuple, np.ndarray)) else
+                 list(range(n - min(int(c), n), n)) for c, n in zip(sample, lens)]      # bool -> 0 / 1 trailing rows
+        if any(r < 0 or r >= n for rows_, n in zip(picks, lens) for r in rows_):
+            raise B200Error("prefill: a wanted row lies outside its chunk")
+        NS = sum(len(c) for c in picks) + Bd
         if NS > self.max_sample:
             raise B200Error(f"prefill step samples {NS} rows, the logits buffer holds {self.max_sample}")
         o_cu = 3 * _align(T)
@@ -551,7 +595,10 @@ class ModelRunner:
         o_dl = o_tq + _align(nt)              # decode rows: sequence lengths
         o_st = o_dl + _align(Bd)              # sampler inputs of the sampled rows: temperatures, seeds
         o_ss = o_st + _align(NS)
-        o_bt = o_ss + _align(NS)
+        o_cua = o_ss + _align(NS)             # every sequence of the step (chunks, then riders): row offsets,
+        o_ctxa = o_cua + _align(S + Bd + 1)   # tokens already in the cache, recurrent-state slot
+        o_sta = o_ctxa + _align(S + Bd)
+        o_bt = o_sta + _align(S + Bd)
         end = o_bt + (S + Bd) * self.max_blocks
         if end > self.stage_words:
             raise B200Error("step inputs exceed the staging buffer")
@@ -568,7 +615,10 @@ class ModelRunner:
             st[o_slots + a:o_slots + b] = tbl[p // bs] * bs + p % bs
         st[o_cu:o_cu + S + 1] = cu
         st[o_ctx:o_ctx + S] = starts
-        sample_rows = [r for s in range(S) for r in range(int(cu[s + 1]) - counts[s], int(cu[s + 1]))]
+        sample_rows = [int(cu[s]) + r for s in range(S) for r in picks[s]]
+        st[o_cua:o_cua + S + 1] = cu
+        st[o_ctxa:o_ctxa + S] = starts
+        st[o_sta:o_sta + S + Bd] = -1 if state_slots is None else np.asarray(state_slots, dtype=np.int32)[:S + Bd]
         if Bd:
             _, last_token, num_computed, dbt = decode
             dpos = np.asarray(num_computed[:Bd], dtype=np.int32)
@@ -576,6 +626,8 @@ class ModelRunner:
             st[o_pos + Tp:o_pos + T] = dpos
             st[o_slots + Tp:o_slots + T] = dbt[np.arange(Bd), dpos // bs] * bs + dpos % bs
             st[o_dl:o_dl + Bd] = dpos + 1
+            st[o_cua + S + 1:o_cua + S + Bd + 1] = Tp + 1 + np.arange(Bd, dtype=np.int32)
+            st[o_ctxa + S:o_ctxa + S + Bd] = dpos
             bt[S:] = dbt[:Bd]
             sample_rows += list(range(Tp, T))
             self.stats["decode_kv_tokens"] += int(dpos.sum()) + Bd
@@ -596,9 +648,29 @@ class ModelRunner:
         ts_d, tq_d = sd[o_ts:o_ts + nt], sd[o_tq:o_tq + nt]
         bt_all = sd[o_bt:end].view(S + Bd, self.max_blocks)
         bt_d = bt_all[:S]
+        dl_d, dbt_d = (sd[o_dl:o_dl + Bd], bt_all[S:]) if Bd else (None, None)
+        self._forward_prefill(ids, T, Tp, Bd, nt, bt_d, cu_d, ctx_d, ts_d, tq_d, dl_d, dbt_d,
+                              sd[o_cua:o_cua + S + Bd + 1], sd[o_ctxa:o_ctxa + S + Bd], sd[o_sta:o_sta + S + Bd])
+        self.stats["prefill_steps"] += 1
+        self.stats["mixed_steps"] = self.stats.get("mixed_steps", 0) + (1 if Bd else 0)
+        self.stats["h2d_bytes"] += end * 4
+        self.stats["d2h_bytes"] += ns * 4
+        self.stats["prefill_tokens"] += Tp
+        if ns == 0:
+            torch.cuda.current_stream().synchronize()
+            return np.zeros(0, dtype=np.int32)
+        self._sample(ns, sd[o_rows:o_rows + ns], sd[o_st:o_st + ns].view(torch.float32), sd[o_ss:o_ss + ns])
+        self.out_host[:ns].copy_(self.out_ids[:ns], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.out_host[:ns].numpy().copy()
+
+    def _forward_prefill(self, ids, T: int, Tp: int, Bd: int, nt: int, bt_d, cu_d, ctx_d, ts_d, tq_d, dl_d, dbt_d,
+                         cu_all, ctx_all, slots_all) -> None:
+        """Embedding + all layers of a prefill / mixed step -> self.xn[:T].  Rows [0, Tp) are the prompt
+        portions (cu_d / ctx_d / tiles / bt_d), rows [Tp, T) the Bd riding decode rows (dl_d / dbt_d);
+        cu_all / ctx_all / slots_all describe both kinds as one list of sequences."""
         self._embed(ids, T)
         if Bd:
-            dl_d, dbt_d = sd[o_dl:o_dl + Bd], bt_all[S:]
             splits, ws = self._decode_attn_plan(Bd)
 
         def attn(l):
@@ -613,18 +685,6 @@ class ModelRunner:
                 self.stats["kernel_launches"] += 1
 
         self._layers(T, attn)
-        self.stats["prefill_steps"] += 1
-        self.stats["mixed_steps"] = self.stats.get("mixed_steps", 0) + (1 if Bd else 0)
-        self.stats["h2d_bytes"] += end * 4
-        self.stats["d2h_bytes"] += ns * 4
-        self.stats["prefill_tokens"] += Tp
-        if ns == 0:
-            torch.cuda.current_stream().synchronize()
-            return np.zeros(0, dtype=np.int32)
-        self._sample(ns, sd[o_rows:o_rows + ns], sd[o_st:o_st + ns].view(torch.float32), sd[o_ss:o_ss + ns])
-        self.out_host[:ns].copy_(self.out_ids[:ns], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self.out_host[:ns].numpy().copy()
 
     # ------------------------------------------------------------------------------ sampling
     def gather_logits_rows(self, rows: Sequence[int]) -> torch.Tensor:

@@ -21,7 +21,7 @@ from typing import Deque, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 
-from .kv_cache import BlockPool, block_digests
+from .kv_cache import BlockPool, StateSlotPool, block_digests
 from .spec_decode import NgramIndex, SpeculativeConfig, verify
 
 
@@ -65,6 +65,7 @@ class Request:
     sample_seed: int = 0           # 32-bit stream id of the in-kernel sampler (params.seed, else drawn at admission)
     digests: List[bytes] = field(default_factory=list)   # chained keys of the full KV blocks
     num_cached_tokens: int = 0     # prompt tokens served from the prefix cache at admission
+    state_slot: int = -1           # recurrent-state slot (models with recurrent mixers), -1 = none
 
     @property
     def all_ids(self) -> List[int]:
@@ -82,6 +83,7 @@ class PrefillPlan:
     starts: List[int]              # first position of each chunk
     lens: List[int]                # tokens in each chunk
     sample: List[bool]             # chunk completes the prompt -> sample a token
+    #                                (a replayed step: the list of the chunk's rows whose logits are wanted)
 
     @property
     def num_tokens(self) -> int:
@@ -127,10 +129,15 @@ class Scheduler:
     def __init__(self, num_blocks: int, block_size: int, max_num_seqs: int, max_num_batched_tokens: int,
                  max_model_len: int, eos_token_id, enable_prefix_caching: bool = False, mixed_steps: bool = True,
                  speculative: Optional[SpeculativeConfig] = None, max_sample_rows: Optional[int] = None,
-                 kv_host_slots: int = 0):
+                 kv_host_slots: int = 0, state_slots: int = 0):
         """eos_token_id: one id, an iterable of ids (every turn terminator of the checkpoint), or None.
         speculative: n-gram speculative decoding on pure decode steps (spec_decode.py); max_sample_rows
         bounds the rows one step may sample (the runner's logits buffer)."""
+        # models with recurrent mixers: one state slot per admitted sequence, and no prefix reuse (a cached
+        # block holds keys and values, not the recurrent state at its end)
+        self.slots: Optional[StateSlotPool] = StateSlotPool(state_slots) if state_slots > 0 else None
+        if self.slots is not None:
+            enable_prefix_caching, kv_host_slots = False, 0
         self.pool = BlockPool(num_blocks, block_size, enable_prefix_caching, host_slots=kv_host_slots)
         self.block_size = block_size
         self.max_num_seqs = max_num_seqs
@@ -161,6 +168,7 @@ class Scheduler:
         # greedy here and re-sampled on the host) and the per-request noise stream
         self.temperature = np.zeros(S, dtype=np.float32)
         self.sample_seed = np.zeros(S, dtype=np.uint32)
+        self.state_slot = np.full(S, -1, dtype=np.int32)
         self._seed_rng = np.random.RandomState(0x5EED)
         self.num_preemptions = 0
         self.spec = speculative if (speculative is not None and speculative.supported) else None
@@ -229,6 +237,9 @@ class Scheduler:
         self.pool.register(r.blocks[:n_full], r.digests[:n_full])
 
     def _release(self, r: Request) -> None:
+        if self.slots is not None and r.state_slot >= 0:
+            self.slots.free(r.state_slot)
+            r.state_slot = -1
         if r.blocks:
             self._publish(r)
             self.pool.free(r.blocks)
@@ -355,6 +366,8 @@ class Scheduler:
             r = self.waiting[0]
             if len(self.rows) + len(self.prefilling) >= self.max_num_seqs:
                 break
+            if self.slots is not None and self.slots.num_free == 0:
+                break
             target = r.prefill_target
             entries: List[tuple] = []        # cached prefix, block by block: (True, device block) | (False, digest in the host tier)
             if self.pool.caching:
@@ -367,6 +380,8 @@ class Scheduler:
             if need + self.pool.count_free(hit) + len(self.rows) > self.pool.num_free:
                 break
             self.waiting.popleft()
+            if self.slots is not None:
+                r.state_slot = self.slots.allocate()
             self.pool.attach(hit)
             self.pool.pin_host([d for on_dev, d in entries if not on_dev])
             fresh = iter(self.pool.allocate(need))
@@ -423,6 +438,32 @@ class Scheduler:
         self.num_preemptions += 1
         self.waiting.appendleft(r)
 
+    # ------------------------------------------------------------------ replay of a given schedule
+    def replay_admit(self, r: Request) -> None:
+        """Admit `r` outside the waiting queue (a replayed trace says which step a request starts in): it takes
+        a state slot now and KV blocks as its tokens arrive (replay_extend)."""
+        if len(self.rows) + len(self.prefilling) >= self.max_num_seqs:
+            raise MemoryError("no free sequence slot")
+        if self.slots is not None:
+            r.state_slot = self.slots.allocate()
+        r.blocks, r.num_computed = [], 0
+        self.prefilling.append(r)
+
+    def replay_extend(self, r: Request, n_new: int) -> None:
+        """KV blocks for the next n_new tokens of `r` (positions num_computed .. num_computed + n_new - 1)."""
+        total = r.num_computed + n_new
+        if total > self.max_model_len:
+            raise ValueError(f"request {r.req_id}: {total} tokens exceed max_model_len ({self.max_model_len})")
+        need = self._blocks_for(total) - len(r.blocks)
+        if need > 0:
+            r.blocks.extend(self.pool.allocate(need))
+
+    def replay_finish(self, r: Request) -> None:
+        if r in self.prefilling:
+            self.prefilling.remove(r)
+        self._release(r)
+        r.finished, r.finish_reason = True, "replayed"
+
     # ------------------------------------------------------------------ persistent batch
     def _install_row(self, r: Request, first_token: int) -> None:
         i = len(self.rows)
@@ -434,6 +475,7 @@ class Scheduler:
         self.check_eos[i] = not r.params.ignore_eos
         self.temperature[i] = kernel_temperature(r.params)
         self.sample_seed[i] = r.sample_seed
+        self.state_slot[i] = r.state_slot
         nb = len(r.blocks)
         self.n_blocks[i] = nb
         self.block_table[i, :nb] = r.blocks
@@ -448,7 +490,7 @@ class Scheduler:
             self.rows[i] = m
             m.row = i
             for a in (self.last_token, self.num_computed, self.remaining, self.check_eos, self.n_blocks,
-                      self.temperature, self.sample_seed):
+                      self.temperature, self.sample_seed, self.state_slot):
                 a[i] = a[last]
             self.block_table[i] = self.block_table[last]
         self.rows.pop()

@@ -328,3 +328,163 @@ def save_checkpoint(cfg: ModelConfig, state: Dict[str, torch.Tensor], out_dir: s
             weight_map[k] = name
     (out / "model.safetensors.index.json").write_text(
         json.dumps({"metadata": {}, "weight_map": weight_map}, indent=1))
+
+
+# ------------------------------------------------------------------------------ layer-list designs
+@dataclass
+class LayerListLayer:
+    """One layer of a layer-list decoder.  Everything that reads the mixer's input is ONE fused projection:
+    attention  rows = [q: H*dk | k: G*dk | v: G*dv | gate: H*dv]   (no k / v rows with kv_from),
+    mlstm      rows = [q: H*dk | k: H*dk | v: H*dv | gate: H*dv];  its two per-head gate projections are a
+    second, fp32-output projection `gates` = [input: H | forget: H]."""
+    norm1: torch.Tensor
+    proj: torch.Tensor
+    o: torch.Tensor
+    proj_bias: Optional[torch.Tensor] = None     # attention: bias of the q (, k, v) rows
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+    sink: Optional[torch.Tensor] = None          # [H] fp32
+    gates: Optional[torch.Tensor] = None         # mlstm: [2H, D]
+    gate_bias: Optional[torch.Tensor] = None     # mlstm: [2H]
+    out_norm: Optional[torch.Tensor] = None      # mlstm: [H*dv]
+    norm2: Optional[torch.Tensor] = None
+    up: Optional[torch.Tensor] = None
+    down: Optional[torch.Tensor] = None
+
+
+@dataclass
+class LayerListWeights:
+    embed: torch.Tensor
+    layers: List[LayerListLayer]
+    final_norm: torch.Tensor
+    lm_head: torch.Tensor
+    vocab_start: int = 0
+    vocab_end: int = 0
+
+
+def layer_list_tensor_shapes(cfg) -> Dict[str, tuple]:
+    """Checkpoint tensor names and shapes of a layer-list model (linear weights are [out, in])."""
+    D = cfg.hidden_size
+    shapes: Dict[str, tuple] = {"embed": (cfg.vocab_size, D), "final.norm": (D,), "head": (cfg.vocab_size, D)}
+    for l, layer in enumerate(cfg.layers):
+        p, m = f"l{l}.", layer.mixer
+        shapes[p + "norm1"] = (D,)
+        if m.kind == "attention":
+            shapes[p + "mix.q"] = (m.q_width, D)
+            if m.qkv_bias:
+                shapes[p + "mix.q.b"] = (m.q_width,)
+            if m.qk_norm:
+                shapes[p + "mix.q.norm"] = (m.dim,)
+            if m.kv_from is None:
+                shapes[p + "mix.k"] = (m.kv_heads * m.dim, D)
+                shapes[p + "mix.v"] = (m.kv_heads * m.vdim, D)
+                if m.qkv_bias:
+                    shapes[p + "mix.k.b"] = (m.kv_heads * m.dim,)
+                    shapes[p + "mix.v.b"] = (m.kv_heads * m.vdim,)
+                if m.qk_norm:
+                    shapes[p + "mix.k.norm"] = (m.dim,)
+            if m.sink:
+                shapes[p + "mix.sink"] = (m.heads,)
+            if m.gate:
+                shapes[p + "mix.g"] = (m.out_width, D)
+            shapes[p + "mix.o"] = (D, m.out_width)
+        else:
+            for n, rows in (("q", m.heads * m.dim), ("k", m.heads * m.dim), ("v", m.out_width), ("g", m.out_width)):
+                shapes[p + "mix." + n] = (rows, D)
+            shapes[p + "mix.o"] = (D, m.out_width)
+            shapes[p + "mix.norm"] = (m.out_width,)
+            for n in ("i", "f"):
+                shapes[p + "mix." + n] = (m.heads, D)
+                shapes[p + "mix." + n + ".b"] = (m.heads,)
+        if layer.mlp is not None:
+            shapes[p + "norm2"] = (D,)
+            shapes[p + "mlp.up"] = (layer.mlp.ff, D)
+            shapes[p + "mlp.down"] = (D, layer.mlp.ff)
+    return shapes
+
+
+def load_layer_list(cfg, get: Callable[[str], torch.Tensor], device: str) -> LayerListWeights:
+    """Fuse the checkpoint tensors of a layer-list model (names as layer_list_tensor_shapes) on `device`.
+    Weights stay bf16 whatever the serving precision: a 32-bit model converts them exactly on the fly."""
+    shapes = layer_list_tensor_shapes(cfg)
+
+    def g(name: str) -> torch.Tensor:
+        t = get(name)
+        if tuple(t.shape) != shapes[name]:
+            raise ValueError(f"{name}: shape {tuple(t.shape)} does not match the config ({shapes[name]})")
+        return t.to(device=device, dtype=BF16)
+
+    def cat(names):
+        return torch.cat([g(n) for n in names], dim=0).contiguous()
+
+    layers = []
+    for l, layer in enumerate(cfg.layers):
+        p, m = f"l{l}.", layer.mixer
+        if m.kind == "attention":
+            own = m.kv_from is None
+            names = ["q"] + (["k", "v"] if own else []) + (["g"] if m.gate else [])
+            lw = LayerListLayer(norm1=g(p + "norm1"), proj=cat([p + "mix." + n for n in names]), o=g(p + "mix.o"))
+            if m.qkv_bias:
+                lw.proj_bias = cat([p + f"mix.{n}.b" for n in (["q", "k", "v"] if own else ["q"])])
+            if m.qk_norm:
+                lw.q_norm = g(p + "mix.q.norm")
+                lw.k_norm = g(p + "mix.k.norm") if own else None
+            if m.sink:
+                lw.sink = g(p + "mix.sink").to(torch.float32).contiguous()
+        else:
+            lw = LayerListLayer(norm1=g(p + "norm1"), proj=cat([p + "mix." + n for n in "qkvg"]), o=g(p + "mix.o"),
+                                gates=cat([p + "mix.i", p + "mix.f"]), gate_bias=cat([p + "mix.i.b", p + "mix.f.b"]),
+                                out_norm=g(p + "mix.norm"))
+        if layer.mlp is not None:
+            lw.norm2, lw.up, lw.down = g(p + "norm2"), g(p + "mlp.up"), g(p + "mlp.down")
+        layers.append(lw)
+    return LayerListWeights(embed=g("embed"), layers=layers, final_norm=g("final.norm"), lm_head=g("head"),
+                            vocab_start=0, vocab_end=cfg.vocab_size)
+
+
+def load_layer_list_dir(cfg, model_path: str, device: str) -> LayerListWeights:
+    from safetensors import safe_open
+
+    files = sorted(Path(model_path).glob("*.safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no *.safetensors files under {model_path}")
+    where: Dict[str, object] = {}
+    for f in files:
+        h = safe_open(str(f), framework="pt")
+        for k in h.keys():
+            where[k] = h
+    return load_layer_list(cfg, lambda name: where[name].get_tensor(name), device)
+
+
+def random_layer_list_state(cfg, seed: int = 0, device: str = "cpu") -> Dict[str, torch.Tensor]:
+    """Seeded bf16 checkpoint of a layer-list model (benchmarks and tests: no trained weights exist).
+    Linear weights N(0, 1/in), biases and sinks of order 1, norm weights 1 + N(0, 0.2), forget-gate
+    biases around +3 so that the recurrent state keeps a long memory."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    out: Dict[str, torch.Tensor] = {}
+    for name, shape in layer_list_tensor_shapes(cfg).items():
+        x = torch.randn(*shape, generator=gen, device=device, dtype=torch.float32)
+        leaf = name.split(".", 1)[1] if name[0] == "l" and name[1].isdigit() else name
+        if leaf.endswith("norm") or leaf in ("norm1", "norm2"):
+            x = 1.0 + 0.2 * x
+        elif leaf == "mix.f.b":
+            x = 3.0 + x
+        elif leaf == "mix.sink":
+            x = 1.5 * x
+        elif leaf.endswith(".b"):
+            x = 0.3 * x if leaf != "mix.i.b" else x
+        elif leaf == "embed":
+            pass
+        else:
+            x = x / (shape[-1] ** 0.5)
+        out[name] = x.to(BF16)
+    return out
+
+
+def save_layer_list_checkpoint(cfg, state: Dict[str, torch.Tensor], out_dir: str) -> None:
+    from safetensors.torch import save_file
+
+    out = Path(out_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    (out / "config.json").write_text(json.dumps(cfg.to_dict(), indent=1))
+    save_file({k: v.detach().to("cpu").contiguous() for k, v in state.items()}, str(out / "model.safetensors"))

@@ -235,6 +235,60 @@ int b200_allreduce_rs_norm_ag(void* const* stage_host, void* const* xn_host, voi
                               int world, int rank, const void* residual, const void* w,
                               void* residual_out, int T, int H, float eps, void* stream);
 
+/* ---- layer-list decoders: norm-after-sum residual stream in fp32, attention with a softmax sink,
+ *      matrix-memory recurrence.  `f32` flags select the element type of activations and caches:
+ *      0 = bf16, 1 = fp32 (a model served in true 32-bit).  Weights are always bf16. ------------- */
+/* y = x W^T (+ bias) on the CUDA cores, fp32 accumulation, no shape or alignment rule. */
+int b200_linear_simt(const void* X, int x_f32, const void* W, const void* bias, void* Y, int y_f32, int M,
+                     int N, int K, int64_t ldx, int64_t ldw, int64_t ldy, void* stream);
+/* z = alpha * x_in[src] + y[r] (z = x_in[src] when y == NULL; src = rows[r] or r), then
+ * o = (z - mean) / sqrt(var + eps) * w * out_scale; x_out (fp32) and xb_out (bf16 / fp32) receive o;
+ * either may be NULL; x_out may alias x_in when rows == NULL. */
+int b200_sum_layer_norm(const void* y, int y_f32, int64_t ldy, const float* x_in, const int32_t* rows,
+                        const void* w, float* x_out, void* xb_out, int xb_f32, int T, int D, float alpha,
+                        float eps, float out_scale, void* stream);
+/* x_out[t] = table[ids[t]] as fp32 (zeros for an id outside [0, V)); xb_out: the same rows as bf16 / fp32. */
+int b200_embed_rows_f32(const int32_t* ids, const void* table, float* x_out, void* xb_out, int xb_f32,
+                        int T, int D, int V, void* stream);
+/* out = max(u, 0)^2 over n elements. */
+int b200_relu2(const void* u, void* out, int f32, int64_t n, void* stream);
+/* Fused projection row = [q: H*dk | k: G*dk | v: G*dv | ...] (q only when has_kv == 0): adds the bias,
+ * RMS-normalises every q and k head (a NULL weight: that side is not normalised), multiplies q by its position's temperature
+ * 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) (temp_every <= 0: none), writes q back in place
+ * and scatters k / v into the paged caches K [blocks][G][page][dk], V [blocks][G][page][dv]. */
+int b200_attn_prep(void* proj, int f32, int64_t ld, const void* bias, const void* qnorm_w,
+                   const void* knorm_w, const int32_t* positions, const int32_t* slots, void* k_cache,
+                   void* v_cache, int T, int H, int G, int dk, int dv, int page, int has_kv, float eps,
+                   float temp_coef, int temp_every, void* stream);
+int b200_attn_sink_prefill_tile(void);
+/* Causal attention of prompt portions over the paged cache; sink [H] fp32 or NULL; gate_col >= 0:
+ * the output is multiplied by sigmoid(proj[t, gate_col + h*dv + d]). */
+int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                           const void* v_cache, const int32_t* block_table, int max_blocks,
+                           const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
+                           const int32_t* tile_q0, int n_tiles, const float* sink, void* out, int64_t ldo,
+                           int H, int G, int dk, int dv, int page, float scale, void* stream);
+/* The same for one new row per sequence (row b of proj / out sees keys [0, seq_lens[b])). */
+int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
+                          const void* v_cache, const int32_t* block_table, int max_blocks,
+                          const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
+                          int G, int dk, int dv, int page, float scale, void* stream);
+/* Column slices Z of a head's state (n and m are kept once per slice). */
+int b200_mlstm_state_slices(int dv);
+/* Stabilised matrix-memory recurrence over each sequence's new rows [cu_seq[s], cu_seq[s+1]); gates
+ * [T][2H] fp32 raw (input | forget) projections, gate_bias [2H] bf16; state of slot state_slots[s]
+ * (S [slots][H][dk][dv], n [slots][H][Z][dk], m [slots][H][Z], fp32) is read unless ctx_lens[s] == 0
+ * and written back; o_raw [T][H*dv] fp32.  Negative slot: the sequence is skipped. */
+int b200_mlstm_scan(const void* proj, int f32, int64_t ld, int q_col, int k_col, int v_col,
+                    const float* gates, const void* gate_bias, const int32_t* cu_seq,
+                    const int32_t* ctx_lens, const int32_t* state_slots, float* S_state, float* n_state,
+                    float* m_state, float* o_raw, int n_seq, int H, int dk, int dv, float cap, float qscale,
+                    void* stream);
+/* out = o_raw / rms_head(o_raw) * norm_w * sigmoid(gate). */
+int b200_mlstm_out(const float* o_raw, const void* proj, int f32, int64_t ld, int gate_col,
+                   const void* norm_w, void* out, int64_t ldo, int T, int H, int dv, float eps,
+                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif
