@@ -57,6 +57,21 @@ __device__ __forceinline__ void load_page(uint8_t* dst, const bf16* __restrict__
   }
 }
 
+// Last step of a decode row: num / den, with the options of mixers that have them -- a softmax SINK (a
+// learned per-head logit that joins the denominator only: den += exp(sink_h - max), the running maximum mm
+// being kept in the base-2 domain) and a sigmoid output gate read from gate[b][h*D + d].
+__device__ __forceinline__ bf16 finish_row(float num, float den, float mm, const float* __restrict__ sink,
+                                           const bf16* __restrict__ gate, int64_t gate_stride, int b, int h, int D,
+                                           int d) {
+  if (sink != nullptr && mm > -INFINITY) den += exp2f(sink[h] * 1.4426950408889634f - mm);
+  float o = den > 0.f ? num / den : 0.f;
+  if (gate != nullptr) {
+    const float gv = __bfloat162float(gate[(size_t)b * gate_stride + (size_t)h * D + d]);
+    o *= 1.f / (1.f + __expf(-gv));
+  }
+  return __float2bfloat16_rn(o);
+}
+
 template <int D>
 __global__ void __launch_bounds__(kDecWarps * 32, 2)
 paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
@@ -64,7 +79,8 @@ paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
                          const int32_t* __restrict__ block_table, int max_blocks,
                          const int32_t* __restrict__ seq_lens, bf16* __restrict__ out,
                          float* __restrict__ ws_o, float* __restrict__ ws_ml, int num_splits,
-                         int Hq, int Hkv, float scale_log2, uint32_t* __restrict__ split_ctr) {
+                         int Hq, int Hkv, float scale_log2, uint32_t* __restrict__ split_ctr,
+                         const float* __restrict__ sink, const bf16* __restrict__ gate, int64_t gate_stride) {
   pdl_launch_dependents();
   pdl_wait();
   using Cfg = DecCfg<D>;
@@ -243,7 +259,7 @@ paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
     }
     const int h = kvh * G + g;
     if (num_splits == 1) {
-      out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      out[((size_t)b * Hq + h) * D + d] = finish_row(num, den, mm, sink, gate, gate_stride, b, h, D, d);
     } else {
       const size_t slot = ((size_t)b * Hq + h) * num_splits + split;
       ws_o[slot * D + d] = num;
@@ -280,7 +296,7 @@ paged_attn_decode_kernel(const bf16* __restrict__ q, int64_t q_stride,
       den += sc * __ldcg(ml + sp * 2 + 1);
       num += sc * __ldcg(ws_o + (row * num_splits + sp) * D + d);
     }
-    out[row * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    out[row * D + d] = finish_row(num, den, mm, sink, gate, gate_stride, b, kvh * G + g, D, d);
   }
 }
 
@@ -699,6 +715,16 @@ extern "C" int b200_paged_attn_decode(const void* q, int64_t q_stride, const voi
                                       int max_blocks, const int32_t* seq_lens, void* out,
                                       void* workspace, int num_splits, int B, int Hq, int Hkv,
                                       int D, int block_size, float scale, void* stream) {
+  return b200_paged_attn_decode_ex(q, q_stride, k_cache, v_cache, block_table, max_blocks, seq_lens, out, workspace,
+                                   num_splits, B, Hq, Hkv, D, block_size, scale, nullptr, nullptr, 0, stream);
+}
+
+extern "C" int b200_paged_attn_decode_ex(const void* q, int64_t q_stride, const void* k_cache,
+                                         const void* v_cache, const int32_t* block_table,
+                                         int max_blocks, const int32_t* seq_lens, void* out,
+                                         void* workspace, int num_splits, int B, int Hq, int Hkv,
+                                         int D, int block_size, float scale, const float* sink,
+                                         const void* gate, int64_t gate_stride, void* stream) {
   B200_REQUIRE(B >= 0 && Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attn_decode: bad head counts");
   B200_REQUIRE(Hq / Hkv <= 16, "attn_decode: group size %d > 16 unsupported", Hq / Hkv);
   B200_REQUIRE(block_size == kPage, "attn_decode: block_size must be %d", kPage);
@@ -725,7 +751,8 @@ extern "C" int b200_paged_attn_decode(const void* q, int64_t q_stride, const voi
     }
     (void)launch_pdl(paged_attn_decode_kernel<128>, dim3(grid), dim3(kDecWarps * 32), DecCfg<128>::kSmemBytes, s, 1, 
         (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
-        max_blocks, seq_lens, (bf16*)out, ws_o, ws_ml, num_splits, Hq, Hkv, scale_log2, split_ctr);
+        max_blocks, seq_lens, (bf16*)out, ws_o, ws_ml, num_splits, Hq, Hkv, scale_log2, split_ctr, sink,
+        (const bf16*)gate, gate_stride);
     rc = b200_check_launch("b200_paged_attn_decode");
   } else {
     static bool once = false;
@@ -736,7 +763,8 @@ extern "C" int b200_paged_attn_decode(const void* q, int64_t q_stride, const voi
     }
     (void)launch_pdl(paged_attn_decode_kernel<64>, dim3(grid), dim3(kDecWarps * 32), DecCfg<64>::kSmemBytes, s, 1, 
         (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
-        max_blocks, seq_lens, (bf16*)out, ws_o, ws_ml, num_splits, Hq, Hkv, scale_log2, split_ctr);
+        max_blocks, seq_lens, (bf16*)out, ws_o, ws_ml, num_splits, Hq, Hkv, scale_log2, split_ctr, sink,
+        (const bf16*)gate, gate_stride);
     rc = b200_check_launch("b200_paged_attn_decode");
   }
   return rc;
@@ -755,8 +783,34 @@ namespace b200 {
 int paged_attn_prefill_tc(const void* q, int64_t q_stride, int num_tokens, const void* k_cache, const void* v_cache,
                           int num_blocks, const int32_t* block_table, int max_blocks, const int32_t* cu_q,
                           const int32_t* ctx_lens, const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles,
-                          void* out, int Hq, int Hkv, int D, float scale, cudaStream_t stream);
+                          void* out, int Hq, int Hkv, int D, float scale, cudaStream_t stream,
+                          const float* sink = nullptr, const void* gate = nullptr, int64_t gate_stride = 0);
 }  // namespace b200
+
+extern "C" int b200_attn_prefill_tc_covers(int Hq, int Hkv, int D) {
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return 0;
+  const int G = Hq / Hkv;
+  return (D == 128 && (G == 4 || G == 8)) ? 1 : 0;
+}
+
+extern "C" int b200_paged_attn_prefill_ex(const void* q, int64_t q_stride, int num_tokens, const void* k_cache,
+                                          const void* v_cache, int num_blocks, const int32_t* block_table,
+                                          int max_blocks, const int32_t* cu_q, const int32_t* ctx_lens,
+                                          const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles, void* out,
+                                          int Hq, int Hkv, int D, int block_size, float scale, const float* sink,
+                                          const void* gate, int64_t gate_stride, void* stream) {
+  B200_REQUIRE(b200_attn_prefill_tc_covers(Hq, Hkv, D), "attn_prefill_ex: heads %d / %d x %d not covered", Hq, Hkv, D);
+  B200_REQUIRE(block_size == kPage, "attn_prefill_ex: block_size must be %d", kPage);
+  if (num_tiles <= 0) return B200_OK;
+  const int rc = paged_attn_prefill_tc(q, q_stride, num_tokens, k_cache, v_cache, num_blocks, block_table, max_blocks,
+                                       cu_q, ctx_lens, tile_seq, tile_q0, num_tiles, out, Hq, Hkv, D, scale,
+                                       (cudaStream_t)stream, sink, gate, gate_stride);
+  if (rc > 0) {
+    b200_set_error("attn_prefill_ex: the tensor-core kernel does not take this call (alignment or device)");
+    return B200_ERR_UNSUPPORTED;
+  }
+  return rc;
+}
 
 extern "C" int b200_paged_attn_prefill(const void* q, int64_t q_stride, int num_tokens, const void* k_cache,
                                        const void* v_cache, int num_blocks, const int32_t* block_table,

@@ -74,7 +74,8 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
                              const int32_t* __restrict__ block_table, int max_blocks,
                              const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_lens,
                              const int32_t* __restrict__ tile_seq, const int32_t* __restrict__ tile_q0,
-                             int num_tiles, bf16* __restrict__ out, int Hq, int Hkv, float scale_log2) {
+                             int num_tiles, bf16* __restrict__ out, int Hq, int Hkv, float scale_log2,
+                             const float* __restrict__ sink, const bf16* __restrict__ gate, int64_t gate_stride) {
   constexpr int TPT = 128 / G;   // query tokens per tile
   extern __shared__ uint8_t fa_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_raw) + 1023) &
@@ -392,16 +393,39 @@ paged_attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       // ---- epilogue: O / l -> bf16 -> out[token, head, :]
       mbar_wait_guarded(o_full, it & 1);
       tc_fence_after();
+      // softmax sink (mixers that have one): a learned per-head logit that joins the denominator only;
+      // l is relative to the reference maximum m_used of the base-2 domain
+      if (sink != nullptr && m_used > -INFINITY) l += exp2f(sink[m.kvh * G + g] * 1.4426950408889634f - m_used);
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* orow = out + ((size_t)(m.q_begin + qi) * Hq + (size_t)(m.kvh * G + g)) * kFaD;
+      // sigmoid output gate (mixers that have one): gate[token][head * D + column], same columns as the row
+      const bf16* grow = (gate != nullptr && valid)
+                             ? gate + (size_t)(m.q_begin + qi) * gate_stride + (size_t)(m.kvh * G + g) * kFaD
+                             : nullptr;
       auto store32 = [&](const uint32_t (&o)[32], bf16* dst) {            // 32 fp32 columns -> 64 bytes of the row
         uint4 wv[4];
+        float f[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(o[i]) * inv;
+        if (grow != nullptr) {
+          const bf16* gp = grow + (dst - orow);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint4 gq = ld_cg_v4(gp + v * 8);      // written by the projection GEMM of this step
+            const uint32_t gw[4] = {gq.x, gq.y, gq.z, gq.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              f[8 * v + 2 * i] *= 1.f / (1.f + __expf(-bf16_lo(gw[i])));
+              f[8 * v + 2 * i + 1] *= 1.f / (1.f + __expf(-bf16_hi(gw[i])));
+            }
+          }
+        }
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
-          wv[v].x = pack_bf16(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
-          wv[v].y = pack_bf16(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
-          wv[v].z = pack_bf16(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
-          wv[v].w = pack_bf16(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+          wv[v].x = pack_bf16(f[8 * v + 0], f[8 * v + 1]);
+          wv[v].y = pack_bf16(f[8 * v + 2], f[8 * v + 3]);
+          wv[v].z = pack_bf16(f[8 * v + 4], f[8 * v + 5]);
+          wv[v].w = pack_bf16(f[8 * v + 6], f[8 * v + 7]);
         }
         if (wide) {
           st_v8(dst, wv[0], wv[1]);
@@ -444,7 +468,7 @@ static int launch_prefill_tc(const void* q, int64_t q_stride, int num_tokens, co
                              const void* v_cache, int num_blocks, const int32_t* block_table, int max_blocks,
                              const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
                              const int32_t* tile_q0, int num_tiles, void* out, int Hq, int Hkv, float scale,
-                             cudaStream_t stream) {
+                             const float* sink, const void* gate, int64_t gate_stride, cudaStream_t stream) {
   auto kernel = paged_attn_prefill_tc_kernel<G, P_TMEM>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -476,7 +500,7 @@ static int launch_prefill_tc(const void* q, int64_t q_stride, int num_tokens, co
   const int grid = (int)(persist ? (total_work < 2LL * sms ? total_work : 2LL * sms) : total_work);
   cudaError_t e = launch_pdl(kernel, dim3(grid), dim3(kFaThreads), (size_t)kFaSmemBytes, stream, 1, tq, tk, tv,
                              block_table, max_blocks, cu_q, ctx_lens, tile_seq, tile_q0, num_tiles, (bf16*)out, Hq,
-                             Hkv, scale_log2);
+                             Hkv, scale_log2, sink, (const bf16*)gate, gate_stride);
   if (e != cudaSuccess) {
     b200_set_error("b200_paged_attn_prefill(tc): launch failed: %s", cudaGetErrorString(e));
     (void)cudaGetLastError();
@@ -490,7 +514,8 @@ static int launch_prefill_tc(const void* q, int64_t q_stride, int num_tokens, co
 int paged_attn_prefill_tc(const void* q, int64_t q_stride, int num_tokens, const void* k_cache, const void* v_cache,
                           int num_blocks, const int32_t* block_table, int max_blocks, const int32_t* cu_q,
                           const int32_t* ctx_lens, const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles,
-                          void* out, int Hq, int Hkv, int D, float scale, cudaStream_t stream) {
+                          void* out, int Hq, int Hkv, int D, float scale, cudaStream_t stream, const float* sink,
+                          const void* gate, int64_t gate_stride) {
   static int enabled = -1;
   if (enabled < 0) {
     const char* e = getenv("B200_ATTN_PREFILL_TC");   // =0: keep the mma.sync kernels (A/B runs)
@@ -500,6 +525,7 @@ int paged_attn_prefill_tc(const void* q, int64_t q_stride, int num_tokens, const
   const DeviceInfo& d = device_info();
   if (!enabled || D != kFaD || (G != 4 && G != 8) || !d.valid || d.cc_major != 10) return 1;
   if (num_tokens <= 0 || num_blocks <= 0 || (q_stride % 8) != 0) return 1;
+  if (gate != nullptr && ((gate_stride % 8) != 0 || (reinterpret_cast<uintptr_t>(gate) & 15))) return 1;
   static int p_tmem = -1;
   if (p_tmem < 0) {
     const char* e = getenv("B200_ATTN_P_TMEM");   // =0: P through shared memory (A/B runs)
@@ -507,7 +533,7 @@ int paged_attn_prefill_tc(const void* q, int64_t q_stride, int num_tokens, const
   }
 #define B200_FA_LAUNCH(GG, PT)                                                                                       \
   launch_prefill_tc<GG, PT>(q, q_stride, num_tokens, k_cache, v_cache, num_blocks, block_table, max_blocks, cu_q,    \
-                            ctx_lens, tile_seq, tile_q0, num_tiles, out, Hq, Hkv, scale, stream)
+                            ctx_lens, tile_seq, tile_q0, num_tiles, out, Hq, Hkv, scale, sink, gate, gate_stride, stream)
   if (G == 4) return p_tmem ? B200_FA_LAUNCH(4, true) : B200_FA_LAUNCH(4, false);
   return p_tmem ? B200_FA_LAUNCH(8, true) : B200_FA_LAUNCH(8, false);
 #undef B200_FA_LAUNCH

@@ -97,6 +97,9 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_addr, const CUten
                                                     int out_f32, int lane, DirectOut dir,
                                                     const float* __restrict__ xs = nullptr, float ws = 1.f) {
   constexpr int CH = BLOCK_X >= 32 ? 32 : 16;
+  // out_f32 carries two flags: bit 0 = fp32 output, bit 1 = squared-ReLU activation before the store
+  const bool relu2 = (out_f32 & 2) != 0;
+  out_f32 &= 1;
 #pragma unroll 1
   for (int c0 = 0; c0 < BLOCK_X; c0 += CH) {
     if (m_base + c0 >= M) break;  // warp-uniform: rest of the tile is padding
@@ -116,6 +119,13 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_addr, const CUten
 #pragma unroll
       for (int j = 0; j < CH; ++j)
         r[j] = __float_as_uint(__uint_as_float(r[j]) * (__shfl_sync(0xffffffffu, xs_lane, j) * ws));
+    }
+    if (relu2) {
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const float v = fmaxf(__uint_as_float(r[j]), 0.f);
+        r[j] = __float_as_uint(v * v);
+      }
     }
     if (dir.ptr != nullptr) {   // warp-uniform
       const int n = n0 + lane;
@@ -590,9 +600,10 @@ gemm_bf16_grouped_2sm_kernel(const __grid_constant__ CUtensorMap tmap_w,
 // Tensor map of the output for the epilogue's TMA stores: [splits][M][N] (bf16, or fp32 when out_f32)
 // or, for the fused SiLU*mul epilogue, the [M][N/2] bf16 activation; box = one warp's chunk.
 template <int BLOCK_X, int EPI>
-static int make_out_tmap(CUtensorMap* ty, void* Y, int M, int N, int64_t ldy, int out_f32, int splits,
+static int make_out_tmap(CUtensorMap* ty, void* Y, int M, int N, int64_t ldy, int out_f32_flags, int splits,
                          DirectOut* dir) {
   constexpr int CH = BLOCK_X >= 32 ? 32 : 16;
+  const int out_f32 = out_f32_flags & 1;      // bit 1 (activation) only concerns the kernel's epilogue
   const int es = (EPI == 1 || !out_f32) ? 2 : 4;
   dir->ptr = nullptr;
   dir->ldy = ldy;
@@ -871,6 +882,12 @@ extern "C" int b200_gemm_bf16_ex(const void* X, const void* W, void* Y, int M, i
       b200_set_error("gemm: block_x=%d unsupported (16,32,64,128,256)", block_x);
       return B200_ERR_INVALID;
   }
+}
+
+extern "C" int b200_gemm_bf16_relu2(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx,
+                                    int64_t ldw, int64_t ldy, void* stream) {
+  // bf16 output (bit 0 clear) with the squared-ReLU flag (bit 1) for the epilogue
+  return b200_gemm_bf16_ex(X, W, Y, M, N, K, ldx, ldw, ldy, 2, 1, 0, stream);
 }
 
 extern "C" int b200_gemm_bf16_silu_mul(const void* X, const void* W, void* Y, int M, int N, int K,

@@ -82,6 +82,12 @@ SIGNATURES = {
                                       _i64, _i32, _i32, _i32, _i32, _i32, _f32, _vp]),
     "b200_attn_sink_decode": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _i64, _i32, _i32,
                                      _i32, _i32, _i32, _f32, _vp]),
+    "b200_attn_prefill_tc_covers": (_i32, [_i32, _i32, _i32]),
+    "b200_paged_attn_prefill_ex": (_i32, [_vp, _i64, _i32, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp,
+                                          _i32, _i32, _i32, _i32, _f32, _vp, _vp, _i64, _vp]),
+    "b200_paged_attn_decode_ex": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _i32, _i32, _i32,
+                                         _i32, _i32, _i32, _f32, _vp, _vp, _i64, _vp]),
+    "b200_gemm_bf16_relu2": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _vp]),
     "b200_mlstm_state_slices": (_i32, [_i32]),
     "b200_mlstm_scan": (_i32, [_vp, _i32, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
                                _i32, _i32, _f32, _f32, _vp]),

@@ -493,7 +493,9 @@ class ModelRunner:
                 self.launches_per_decode = self.stats["kernel_launches"] - k0
                 torch.cuda.synchronize()
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, pool=self.graph_pool, stream=s):
+                # thread_local: a CUDA call made by ANOTHER thread of the process (a server thread, an allocator
+                # trimming pinned memory) while this one records must not invalidate the capture
+                with torch.cuda.graph(g, pool=self.graph_pool, stream=s, capture_error_mode="thread_local"):
                     self._decode_forward(B)
                 if self.graph_pool is None:
                     self.graph_pool = g.pool()

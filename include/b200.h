@@ -273,6 +273,26 @@ int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int gate_col, c
                           const void* v_cache, const int32_t* block_table, int max_blocks,
                           const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
                           int G, int dk, int dv, int page, float scale, void* stream);
+/* The tensor-core kernels of the Llama-class models with the same two options, for mixers whose key and
+ * value widths are equal and a tile size (decode: D 64 / 128; prefill: D 128, group of 4 or 8, tiles of
+ * b200_attn_prefill_tile rows): sink [Hq] fp32 or NULL joins the softmax denominator, gate (bf16,
+ * [rows][gate_stride], columns h*D + d) or NULL multiplies the output by its sigmoid. */
+int b200_attn_prefill_tc_covers(int Hq, int Hkv, int D);
+int b200_paged_attn_prefill_ex(const void* q, int64_t q_stride, int num_tokens, const void* k_cache,
+                               const void* v_cache, int num_blocks, const int32_t* block_table,
+                               int max_blocks, const int32_t* cu_q, const int32_t* ctx_lens,
+                               const int32_t* tile_seq, const int32_t* tile_q0, int num_tiles, void* out,
+                               int Hq, int Hkv, int D, int block_size, float scale, const float* sink,
+                               const void* gate, int64_t gate_stride, void* stream);
+int b200_paged_attn_decode_ex(const void* q, int64_t q_stride, const void* k_cache,
+                              const void* v_cache, const int32_t* block_table,
+                              int max_blocks, const int32_t* seq_lens, void* out,
+                              void* workspace, int num_splits, int B, int Hq, int Hkv,
+                              int D, int block_size, float scale, const float* sink,
+                              const void* gate, int64_t gate_stride, void* stream);
+/* y = max(x W^T, 0)^2 in the tcgen05 GEMM's epilogue (bf16 in and out; same shape rules as b200_gemm_bf16). */
+int b200_gemm_bf16_relu2(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx,
+                         int64_t ldw, int64_t ldy, void* stream);
 /* Column slices Z of a head's state (n and m are kept once per slice). */
 int b200_mlstm_state_slices(int dv);
 /* Stabilised matrix-memory recurrence over each sequence's new rows [cu_seq[s], cu_seq[s+1]); gates
