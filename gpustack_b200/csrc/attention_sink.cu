@@ -84,8 +84,9 @@ attn_prep_kernel(TA* proj, int64_t ld, const bf16* __restrict__ bias, const bf16
 // -------------------------------------------------------------------------------------- prefill
 constexpr int kPfRows = 16, kPfKeys = 32, kPfWarps = 4, kPfRowsPerWarp = kPfRows / kPfWarps;
 
-// grid (tiles, H).  Tile i = rows [tile_q0[i], +16) of sequence tile_seq[i]; the sequence's new rows
-// are cu_q[s] .. cu_q[s+1]) of the projection and sit at positions ctx_lens[s] + row.
+// grid (tiles, H, tile_rows / 16).  Tile i = rows [tile_q0[i], +tile_rows) of sequence tile_seq[i], cut into
+// 16-row pieces along z; the sequence's new rows are [cu_q[s], cu_q[s+1]) of the projection and sit at
+// positions ctx_lens[s] + row.
 template <typename TA>
 __global__ void __launch_bounds__(kPfWarps * 32)
 attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, const TA* __restrict__ k_cache,
@@ -100,8 +101,9 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
   float* Vs = Ks + kPfKeys * (dk + 1);                // [32][dv]
   float* Ps = Vs + kPfKeys * dv;                      // [4 warps][4 rows][32]
   const int tile = blockIdx.x, h = blockIdx.y, g = h / (H / G);
-  const int s = tile_seq[tile], q0 = tile_q0[tile];
+  const int s = tile_seq[tile], q0 = tile_q0[tile] + kPfRows * blockIdx.z;
   const int row0 = cu_q[s], qlen = cu_q[s + 1] - row0, ctx = ctx_lens[s];
+  if (q0 >= qlen) return;                             // a piece beyond the end of a short last tile
   const int nrows = min(kPfRows, qlen - q0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int32_t* bt = block_table + (size_t)s * max_blocks;
@@ -310,8 +312,10 @@ extern "C" int b200_attn_sink_prefill_tile(void) { return kPfRows; }
 extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
                                       const void* v_cache, const int32_t* block_table, int max_blocks,
                                       const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
-                                      const int32_t* tile_q0, int n_tiles, const float* sink, void* out, int64_t ldo,
-                                      int H, int G, int dk, int dv, int page, float scale, void* stream) {
+                                      const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
+                                      int64_t ldo, int H, int G, int dk, int dv, int page, float scale, void* stream) {
+  B200_REQUIRE(tile_rows > 0 && tile_rows % kPfRows == 0, "attn_sink_prefill: tiles of %d rows (multiples of %d)",
+               tile_rows, kPfRows);
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 32 * kMaxDvPerLane && page > 0,
                "attn_sink_prefill: bad shape H=%d G=%d dk=%d dv=%d", H, G, dk, dv);
   if (n_tiles <= 0) return B200_OK;
@@ -319,7 +323,7 @@ extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int
                                        (size_t)kPfWarps * kPfRowsPerWarp * 32);
   B200_REQUIRE(smem <= 200 * 1024, "attn_sink_prefill: head widths %d / %d exceed shared memory", dk, dv);
   cudaStream_t s = (cudaStream_t)stream;
-  dim3 grid(n_tiles, H);
+  dim3 grid(n_tiles, H, tile_rows / kPfRows);
   if (f32) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(attn_sink_prefill_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

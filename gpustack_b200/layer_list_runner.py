@@ -38,8 +38,24 @@ class LayerListRunner(ModelRunner):
         if self.tp != 1:
             raise B200Error("layer-list models run with tensor_parallel_size=1")
         self.act_dtype = torch.float32 if self.ecfg.dtype == "float32" else BF16
-        self.prefill_tile = ops.attn_sink_prefill_tile()
         self.fp8 = False
+        # attention layers whose keys and values have one tile-sized width run on the tensor-core kernels of the
+        # Llama-class models (extended with the sink and the gate); the others on the generic kernels
+        bf = self.act_dtype == BF16
+        attn = [(l, x.mixer) for l, x in enumerate(cfg.layers) if x.mixer.kind == "attention"]
+        self.fast_decode = {l: bf and m.dim == m.vdim and m.dim in (64, 128) and m.heads // m.kv_heads <= 16 for l, m in attn}
+        self.fast_prefill = {l: bf and m.dim == m.vdim and ops.attn_prefill_tc_covers(m.heads, m.kv_heads, m.dim)
+                             for l, m in attn}
+        base = ops.attn_sink_prefill_tile()
+        # ONE tile list serves every layer of a step: the tile size most tensor-core layers want (ties: the larger)
+        tiles = [ops.attn_prefill_tile(m.heads, m.kv_heads) for l, m in attn if self.fast_prefill[l]]
+        self.prefill_tile = max(set(tiles), key=lambda t: (tiles.count(t), t)) if tiles else base
+        for l, m in attn:
+            if self.fast_prefill[l] and ops.attn_prefill_tile(m.heads, m.kv_heads) != self.prefill_tile:
+                self.fast_prefill[l] = False
+        if self.prefill_tile % base:
+            raise B200Error("prefill tile sizes of the attention kernels do not nest")
+        self._dec_ws = {}
         self.proj_width = max(lw.proj.shape[0] for lw in self.w.layers)
         self.mix_width = max(l.mixer.out_width for l in cfg.layers)
         self.ff_width = max([l.mlp.ff for l in cfg.layers if l.mlp is not None] or [0])
@@ -116,6 +132,20 @@ class LayerListRunner(ModelRunner):
         ops.sum_layer_norm(self.y[:T], self.resid32[:T], norm_w, cfg.postln_alpha, cfg.norm_eps,
                            x_out=self.resid32[:T], xb_out=self.xb[:T])
 
+    def _decode_plan(self, B: int, m):
+        """(KV splits, workspace) of the split-KV decode kernel for B rows of mixer m; one zero-initialised,
+        self-resetting workspace per head shape, sized for the largest batch."""
+        splits = ops.attn_decode_splits(B, m.kv_heads, self.max_model_len)
+        key = (m.heads, m.kv_heads, m.dim)
+        if key not in self._dec_ws:
+            from .lib import load
+
+            L = load()
+            need = max(L.b200_attn_decode_workspace_bytes(b, m.heads, m.dim, ops.attn_decode_splits(b, m.kv_heads, self.max_model_len))
+                       for b in range(1, self.max_seqs + 1))
+            self._dec_ws[key] = torch.zeros((need + 3) // 4, dtype=torch.float32, device=self.device)
+        return splits, self._dec_ws[key]
+
     def _run_layers(self, T: int, Tp: int, Bd: int, nt: int, bt_p, cu_p, ctx_p, ts, tq, lens_d, bt_d, cu_all, ctx_all,
                     slots_all) -> None:
         """Rows [0, Tp): prompt portions (tiles ts / tq over cu_p / ctx_p / bt_p); rows [Tp, T): Bd single new
@@ -134,10 +164,18 @@ class LayerListRunner(ModelRunner):
                               self.v_cache[l] if own else None, H, G, dk, dv, eps, m.q_temp_coef, m.q_temp_every)
                 gate_col = (H * dk + (G * (dk + dv) if own else 0)) if m.gate else -1
                 kc, vc = self.k_cache[l], self.v_cache[l]
-                if nt:
+                if nt and self.fast_prefill[l]:
+                    ops.paged_attn_prefill_ex(proj[:Tp], proj.stride(0), kc, vc, bt_p, cu_p, ctx_p, ts, tq, out[:Tp], H, G, dk,
+                                              m.scale, sink=lw.sink, gate=proj[:Tp, gate_col:] if m.gate else None)
+                elif nt:
                     ops.attn_sink_prefill(proj[:Tp], gate_col, kc, vc, bt_p, cu_p, ctx_p, ts, tq, lw.sink, out[:Tp],
-                                          H, G, dk, dv, m.scale)
-                if Bd:
+                                          H, G, dk, dv, m.scale, tile_rows=self.prefill_tile)
+                if Bd and self.fast_decode[l]:
+                    splits, ws = self._decode_plan(Bd, m)
+                    ops.paged_attn_decode(proj[Tp:T], proj.stride(0), kc, vc, bt_d, lens_d, out[Tp:T], H, G, dk, m.scale,
+                                          num_splits=splits, workspace=ws, sink=lw.sink,
+                                          gate=proj[Tp:T, gate_col:] if m.gate else None)
+                elif Bd:
                     ops.attn_sink_decode(proj[Tp:T], gate_col, kc, vc, bt_d, lens_d, lw.sink, out[Tp:T], H, G, dk, dv,
                                          m.scale)
                 self.stats["kernel_launches"] += 2 + (1 if nt else 0) + (1 if Bd else 0)
@@ -156,11 +194,10 @@ class LayerListRunner(ModelRunner):
             self.stats["kernel_launches"] += 2
             if layer.mlp is not None:
                 act = self._view(self.act, T, layer.mlp.ff)
-                ops.linear(self.xb[:T], lw.up, act)
-                ops.relu2(act)
+                ops.linear(self.xb[:T], lw.up, act, relu2=True)        # squared ReLU in the GEMM's epilogue
                 ops.linear(act, lw.down, self.y[:T])
                 self._post(T, lw.norm2)
-                self.stats["kernel_launches"] += 4
+                self.stats["kernel_launches"] += 3
 
     def _forward_decode(self, ids, B: int, bt, lens, state_slots) -> None:
         if self.mcfg.has_state and self.num_state_slots == 0:

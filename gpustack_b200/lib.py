@@ -78,7 +78,7 @@ SIGNATURES = {
     "b200_attn_prep": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32,
                               _i32, _f32, _f32, _i32, _vp]),
     "b200_attn_sink_prefill_tile": (_i32, []),
-    "b200_attn_sink_prefill": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp, _vp,
+    "b200_attn_sink_prefill": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp,
                                       _i64, _i32, _i32, _i32, _i32, _i32, _f32, _vp]),
     "b200_attn_sink_decode": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _i64, _i32, _i32,
                                      _i32, _i32, _i32, _f32, _vp]),

@@ -364,13 +364,15 @@ def attn_decode_workspace(B, Hq, D, num_splits, device) -> torch.Tensor:
 
 
 def paged_attn_decode(q, q_stride, k_cache, v_cache, block_table, seq_lens, out, Hq, Hkv, D, scale,
-                      num_splits=1, workspace=None):
-    """q: [B, >=Hq*D] view into the qkv buffer (row stride q_stride elements)."""
+                      num_splits=1, workspace=None, sink=None, gate=None):
+    """q: [B, >=Hq*D] view into the qkv buffer (row stride q_stride elements).  sink [Hq] fp32: softmax sink;
+    gate [B, >=Hq*D] bf16 view (same row stride rule): the output is multiplied by sigmoid(gate)."""
     B = seq_lens.shape[0]
     _req(block_table, torch.int32, "block_table"); _req(seq_lens, torch.int32, "seq_lens")
-    check(load().b200_paged_attn_decode(_p(q), q_stride, _p(k_cache), _p(v_cache), _p(block_table),
-                                        block_table.shape[1], _p(seq_lens), _p(out), _p(workspace),
-                                        num_splits, B, Hq, Hkv, D, k_cache.shape[2], scale, _stream()),
+    check(load().b200_paged_attn_decode_ex(_p(q), q_stride, _p(k_cache), _p(v_cache), _p(block_table),
+                                           block_table.shape[1], _p(seq_lens), _p(out), _p(workspace),
+                                           num_splits, B, Hq, Hkv, D, k_cache.shape[2], scale, _p(sink), _p(gate),
+                                           0 if gate is None else gate.stride(0), _stream()),
           "paged_attn_decode")
     return out
 
@@ -393,6 +395,22 @@ def build_prefill_tiles(q_lens: Sequence[int], tile: int, ctx_lens: Optional[Seq
             tiles.append((c + q0 + tile, s, q0))
     tiles.sort(key=lambda t: -t[0])
     return [t[1] for t in tiles], [t[2] for t in tiles]
+
+
+def attn_prefill_tc_covers(Hq, Hkv, D) -> bool:
+    return bool(load().b200_attn_prefill_tc_covers(Hq, Hkv, D))
+
+
+def paged_attn_prefill_ex(q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, out, Hq, Hkv, D,
+                          scale, sink=None, gate=None):
+    """The tcgen05 prefill kernel with a softmax sink ([Hq] fp32) and / or a sigmoid output gate (bf16 view
+    [T, >=Hq*D]); only for shapes attn_prefill_tc_covers() accepts, tiles of attn_prefill_tile(Hq, Hkv) rows."""
+    check(load().b200_paged_attn_prefill_ex(_p(q), q_stride, q.shape[0], _p(k_cache), _p(v_cache), k_cache.shape[0],
+                                            _p(block_table), block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq),
+                                            _p(tile_q0), tile_seq.shape[0], _p(out), Hq, Hkv, D, k_cache.shape[2], scale,
+                                            _p(sink), _p(gate), 0 if gate is None else gate.stride(0), _stream()),
+          "paged_attn_prefill_ex")
+    return out
 
 
 def paged_attn_prefill(q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0,
@@ -422,8 +440,8 @@ def _cuda(*ts) -> None:
             raise B200Error("expected CUDA tensors (there is no CPU path)")
 
 
-def linear(x, w, out, bias=None):
-    """out = x @ w.T (+ bias).  bf16 x / bf16 or fp32 out with K a multiple of 64 and 16-byte aligned rows
+def linear(x, w, out, bias=None, relu2: bool = False):
+    """out = x @ w.T (+ bias); relu2: out = max(., 0)^2 (in the GEMM's epilogue on the tensor-core path).  bf16 x / bf16 or fp32 out with K a multiple of 64 and 16-byte aligned rows
     go to the tcgen05 GEMM; every other case (fp32 activations = a model served in true 32-bit; odd
     shapes) runs on the CUDA cores with fp32 FMA accumulation."""
     _cuda(x, w, out, bias)
@@ -435,10 +453,25 @@ def linear(x, w, out, bias=None):
     if (not xf and bias is None and K % 64 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
             and (out.stride(0) * out.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0
             and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
-        return gemm(x, w, out=out, out_dtype=out.dtype)
+        if not relu2:
+            return gemm(x, w, out=out, out_dtype=out.dtype)
+        if not yf:
+            timed = TIMER is not None and not torch.cuda.is_current_stream_capturing()
+            if timed:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            check(load().b200_gemm_bf16_relu2(_p(x), _p(w), _p(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+                                              _stream()), "gemm_relu2")
+            if timed:
+                e1.record()
+                TIMER.records.append(("gemm_prefill" if M > 256 else "gemm_decode", 2.0 * M * N * K,
+                                      2.0 * (N * K + M * K) + 2.0 * M * N, e0, e1))
+            return out
+        gemm(x, w, out=out, out_dtype=out.dtype)
+        return relu2_(out)
     check(load().b200_linear_simt(_p(x), xf, _p(w), _p(bias), _p(out), yf, M, N, K, x.stride(0), w.stride(0),
                                   out.stride(0), _stream()), "linear_simt")
-    return out
+    return relu2_(out) if relu2 else out
 
 
 def sum_layer_norm(y, x_in, w, alpha: float, eps: float, x_out=None, xb_out=None, rows=None, out_scale: float = 1.0):
@@ -459,6 +492,10 @@ def embed_rows(ids, table, x_out, xb_out=None):
     _req(ids, torch.int32, "ids"); _req(table, torch.bfloat16, "table"); _req(x_out, torch.float32, "x_out")
     check(load().b200_embed_rows_f32(_p(ids), _p(table), _p(x_out), _p(xb_out), 0 if xb_out is None else _is_f32(xb_out),
                                      ids.shape[0], table.shape[1], table.shape[0], _stream()), "embed_rows")
+
+
+def relu2_(u):
+    return relu2(u)
 
 
 def relu2(u, out=None):
@@ -487,13 +524,14 @@ def attn_sink_prefill_tile() -> int:
 
 
 def attn_sink_prefill(proj, gate_col, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out,
-                      H, G, dk, dv, scale):
+                      H, G, dk, dv, scale, tile_rows: int = 0):
     _cuda(proj, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out)
     if k_cache.dtype != proj.dtype or out.dtype != proj.dtype:
         raise B200Error("attn_sink_prefill: projection, cache and output must share one element type")
     check(load().b200_attn_sink_prefill(_p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(k_cache), _p(v_cache),
                                         _p(block_table), block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq),
-                                        _p(tile_q0), tile_seq.shape[0], _p(sink), _p(out), out.stride(0), H, G, dk, dv,
+                                        _p(tile_q0), tile_seq.shape[0], tile_rows or attn_sink_prefill_tile(), _p(sink),
+                                        _p(out), out.stride(0), H, G, dk, dv,
                                         k_cache.shape[2], scale, _stream()), "attn_sink_prefill")
     return out
 

@@ -261,13 +261,14 @@ int b200_attn_prep(void* proj, int f32, int64_t ld, const void* bias, const void
                    void* v_cache, int T, int H, int G, int dk, int dv, int page, int has_kv, float eps,
                    float temp_coef, int temp_every, void* stream);
 int b200_attn_sink_prefill_tile(void);
-/* Causal attention of prompt portions over the paged cache; sink [H] fp32 or NULL; gate_col >= 0:
+/* Causal attention of prompt portions over the paged cache, tiles of tile_rows rows (a multiple of
+ * b200_attn_sink_prefill_tile()); sink [H] fp32 or NULL; gate_col >= 0:
  * the output is multiplied by sigmoid(proj[t, gate_col + h*dv + d]). */
 int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
                            const void* v_cache, const int32_t* block_table, int max_blocks,
                            const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
-                           const int32_t* tile_q0, int n_tiles, const float* sink, void* out, int64_t ldo,
-                           int H, int G, int dk, int dv, int page, float scale, void* stream);
+                           const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
+                           int64_t ldo, int H, int G, int dk, int dv, int page, float scale, void* stream);
 /* The same for one new row per sequence (row b of proj / out sees keys [0, seq_lens[b])). */
 int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
                           const void* v_cache, const int32_t* block_table, int max_blocks,

@@ -50,6 +50,19 @@ def cfg_tiles():
                        {"type": "mlstm", "mixer": {"heads": 4, "dim": 16, "vdim": 48, "gate_cap": 20.0}, "mlp": {"kind": "dense", "ff": 64}}]}
 
 
+def cfg_tc():
+    """Equal key / value widths of a tensor-core tile: in bf16 the first attention layer (128 wide, groups of 4) runs on the
+    tcgen05 prefill kernel and the split-KV decode kernel with sink and gate; the second (groups of 8: another tile size)
+    and the third (64 wide) keep the generic prefill kernel, with 32-row tiles cut in two, and the fast decode kernel."""
+    return {"architecture": "Vodavik", "vocab": 320, "width": 256, "postln_alpha": 2.0, "logit_scale": 0.7,
+            "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention", "mixer": _attn(8, 2, 128, 128, every=16, coef=0.3), "mlp": {"kind": "dense", "ff": 256}},
+                       {"type": "mlstm", "mixer": {"heads": 2, "dim": 64, "vdim": 96, "gate_cap": 10.0}, "mlp": None},
+                       {"type": "attention", "mixer": _attn(8, 1, 128, 128), "mlp": None},
+                       {"type": "attention", "mixer": _attn(4, 2, 64, 64, every=7, coef=0.5), "mlp": {"kind": "dense", "ff": 128}},
+                       {"type": "attention", "mixer": _attn(8, 2, 128, 128, kv_from=0), "mlp": None}]}
+
+
 def _engine(cfg, weights, dtype, blocks=64, seqs=4, mbt=256, eager=False):
     from gpustack_b200.config import EngineConfig, LayerListConfig
     from gpustack_b200.engine import LLMEngine
@@ -296,10 +309,19 @@ def test_mlstm_out_norm_gate():
 
 
 # ------------------------------------------------------------------------------------ the engine
-@pytest.fixture(scope="module", params=["odd", "tiles"])
+@pytest.fixture(scope="module", params=["odd", "tiles", "tc"])
 def model(request):
-    cfg = cfg_odd() if request.param == "odd" else cfg_tiles()
-    return cfg, O.random_weights(cfg, seed=11 if request.param == "odd" else 12)
+    cfg = {"odd": cfg_odd, "tiles": cfg_tiles, "tc": cfg_tc}[request.param]()
+    return cfg, O.random_weights(cfg, seed={"odd": 11, "tiles": 12, "tc": 13}[request.param])
+
+
+def test_tensor_core_attention_is_chosen_where_the_shapes_allow():
+    cfg = cfg_tc()
+    r = _engine(cfg, O.random_weights(cfg, seed=1), "bfloat16").runner
+    assert r.prefill_tile == 32 and r.fast_prefill == {0: True, 2: False, 3: False, 4: True}
+    assert all(r.fast_decode.values())
+    r = _engine(cfg, O.random_weights(cfg, seed=1), "float32").runner
+    assert not any(r.fast_prefill.values()) and not any(r.fast_decode.values()) and r.prefill_tile == 16
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
