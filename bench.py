@@ -67,6 +67,11 @@ def parse_args():
     ap.add_argument("--cpu-sample-output", type=int, default=16)
     ap.add_argument("--no-cpu-configs0", action="store_true",
                     help="skip the BASELINE configs[0] CPU leg (Qwen2-0.5B shape, 32 requests on the host cores)")
+    ap.add_argument("--family", default=None, choices=[None, "vodavik"],
+                    help="side benchmark of another model family beside the closest Llama-class model of equal layer "
+                         "sizes (prefill / decode tokens per second and per-kernel roofline fractions); prints its own "
+                         "JSON line and leaves the default workload alone")
+    ap.add_argument("--family-sizes", default="2k,4k")
     return ap.parse_args()
 
 
@@ -718,6 +723,11 @@ def finish_ours(a, res):
 
 def main():
     a = parse_args()
+    if a.family:
+        from gpustack_b200 import family_bench
+
+        print(json.dumps(family_bench.run(sizes=tuple(a.family_sizes.split(",")), log=log)), flush=True)
+        return 0
     if a.impl == "reference":
         run_reference(a)
         return 0
