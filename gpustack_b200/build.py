@@ -42,6 +42,16 @@ LAYER_LIST_SOURCES = [
     "attention_sink.cu",
     "mlstm.cu",
 ]
+# ... plus the tensor-core attention kernels when some attention layer has tile-sized heads
+ATTENTION_TC_SOURCES = ["attention.cu", "attention_prefill_tc.cu"]
+
+
+def layer_list_sources(mcfg):
+    """(tag, sources) of the library a process serving this layer-list model needs."""
+    tc = any(l.mixer.kind == "attention" and l.mixer.tile_sized for l in mcfg.layers)
+    return ("layer_list_tc", LAYER_LIST_SOURCES + ATTENTION_TC_SOURCES) if tc else ("layer_list", list(LAYER_LIST_SOURCES))
+
+
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

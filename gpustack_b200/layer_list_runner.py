@@ -43,9 +43,8 @@ class LayerListRunner(ModelRunner):
         # Llama-class models (extended with the sink and the gate); the others on the generic kernels
         bf = self.act_dtype == BF16
         attn = [(l, x.mixer) for l, x in enumerate(cfg.layers) if x.mixer.kind == "attention"]
-        self.fast_decode = {l: bf and m.dim == m.vdim and m.dim in (64, 128) and m.heads // m.kv_heads <= 16 for l, m in attn}
-        self.fast_prefill = {l: bf and m.dim == m.vdim and ops.attn_prefill_tc_covers(m.heads, m.kv_heads, m.dim)
-                             for l, m in attn}
+        self.fast_decode = {l: bf and m.tile_sized for l, m in attn}
+        self.fast_prefill = {l: bf and m.tile_sized and ops.attn_prefill_tc_covers(m.heads, m.kv_heads, m.dim) for l, m in attn}
         base = ops.attn_sink_prefill_tile()
         # ONE tile list serves every layer of a step: the tile size most tensor-core layers want (ties: the larger)
         tiles = [ops.attn_prefill_tile(m.heads, m.kv_heads) for l, m in attn if self.fast_prefill[l]]

@@ -38,7 +38,7 @@ def run(model: str, dtype: str, out_dir: str, max_tokens: int, max_seqs: int = 4
         print("this model family has no 32-bit path", file=sys.stderr)
         return 3
     if family == "layer_list":
-        lib.prefer_subset("layer_list", build.LAYER_LIST_SOURCES)     # a fresh checkout compiles this family's kernels only
+        lib.prefer_subset(*build.layer_list_sources(mcfg))     # a fresh checkout compiles what this model launches, no more
     import torch
 
     from .engine import LLMEngine

@@ -145,3 +145,31 @@ def test_oracle_recurrence_and_attention_do_not_depend_on_the_cut():
     assert torch.allclose(none[0], v[0], atol=1e-12) and not torch.allclose(full[0], v[0])
     t = O.query_temperature(torch.tensor([0, 1, 2, 3, 5, 8]), 0.5, 3)
     assert torch.allclose(t, 1 + 0.5 * torch.log(torch.tensor([1.0, 1.0, 2.0, 2.0, 3.0, 4.0], dtype=torch.float64)))
+
+
+def test_family_libraries_link_alone_and_export_what_the_runner_calls():
+    """A process that serves one layer-list model builds a library from that family's sources only; both variants
+    (generic attention only / plus the tensor-core attention kernels) must link without the rest and export every
+    entry point the runner can reach for such a model."""
+    import ctypes
+
+    from gpustack_b200 import build
+
+    generic = LayerListConfig.from_dict(_cfg())
+    tag, srcs = build.layer_list_sources(generic)
+    assert tag == "layer_list" and "attention.cu" not in srcs and "moe.cu" not in srcs
+    d = _cfg()
+    d["layers"][1]["mixer"].update(dim=64, vdim=64)
+    d["layers"][2]["mixer"].update(dim=64, vdim=64)
+    tag_tc, srcs_tc = build.layer_list_sources(LayerListConfig.from_dict(d))
+    assert tag_tc == "layer_list_tc" and set(build.ATTENTION_TC_SOURCES) <= set(srcs_tc)
+    base = ["b200_linear_simt", "b200_gemm_bf16_ex", "b200_gemm_bf16_relu2", "b200_sum_layer_norm", "b200_embed_rows_f32",
+            "b200_relu2", "b200_attn_prep", "b200_attn_sink_prefill", "b200_attn_sink_decode", "b200_mlstm_scan",
+            "b200_mlstm_out", "b200_sample_f32", "b200_last_error"]
+    for t, s_, names in ((tag, srcs, base), (tag_tc, srcs_tc, base + ["b200_paged_attn_prefill_ex", "b200_paged_attn_decode_ex",
+                                                                      "b200_attn_prefill_tile", "b200_attn_decode_splits",
+                                                                      "b200_attn_decode_workspace_bytes"])):
+        h = ctypes.CDLL(str(build.build(sources=s_, tag=t)))
+        for n in names:
+            assert hasattr(h, n), (t, n)
+    assert not hasattr(ctypes.CDLL(str(build.subset_lib(tag))), "b200_moe_route")
