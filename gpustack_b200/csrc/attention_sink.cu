@@ -28,55 +28,85 @@ __device__ __forceinline__ void as_store(bf16* p, float v) { *p = __float2bfloat
 constexpr int kMaxDvPerLane = 8;   // value width <= 256
 
 // ----------------------------------------------------------------------------------------- prep
-// grid (T, H + 2G) (or (T, H) for a layer that reuses another layer's keys and values); one warp each.
-template <typename TA>
-__global__ void __launch_bounds__(32)
+// One warp per (token, head slot): slots [0, H) are query heads, [H, H + G) key heads, [H + G, H + 2G) value
+// heads (a layer that reuses another layer's keys and values has query slots only).  8 warps per CTA.  Each
+// lane keeps its elements (two neighbours per step) in registers between the sum of squares and the
+// store, so the row is read once.  Widths up to 512.
+constexpr int kPrepWarps = 8, kPrepPairs = 8;
+
+__device__ __forceinline__ float2 ld_pair(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 ld_pair(const bf16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const bf162*>(p));
+}
+__device__ __forceinline__ void st_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void st_pair(bf16* p, float a, float b) {
+  *reinterpret_cast<bf162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// PAIR: every width, column offset and leading dimension is even (2-element loads and stores)
+template <typename TA, bool PAIR>
+__global__ void __launch_bounds__(kPrepWarps * 32)
 attn_prep_kernel(TA* proj, int64_t ld, const bf16* __restrict__ bias, const bf16* __restrict__ qnorm_w,
                  const bf16* __restrict__ knorm_w, const int32_t* __restrict__ positions,
                  const int32_t* __restrict__ slots, TA* k_cache, TA* v_cache, int H, int G, int dk, int dv, int page,
-                 float eps, float temp_coef, int temp_every) {
-  const int t = blockIdx.x, hs = blockIdx.y, lane = threadIdx.x;
+                 int n_slots, float eps, float temp_coef, int temp_every) {
+  const int t = blockIdx.x, hs = blockIdx.y * kPrepWarps + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (hs >= n_slots) return;
   TA* row = proj + (size_t)t * ld;
-  if (hs < H + G) {
-    // a query head (hs < H) or a key head: bias, unit RMS over the head, weight, (temperature)
-    const bool is_q = hs < H;
-    const int col0 = hs * dk;                       // q heads then k heads are contiguous, both dk wide
-    const bf16* w = is_q ? qnorm_w : knorm_w;
-    float ss = 0.f;
-    for (int d = lane; d < dk; d += 32) {
-      float v = as_f32(row[col0 + d]);
-      if (bias != nullptr) v += __bfloat162float(bias[col0 + d]);
-      ss = fmaf(v, v, ss);
+  const bool is_q = hs < H, is_k = !is_q && hs < H + G;
+  const int width = (is_q || is_k) ? dk : dv;
+  const int col0 = (is_q || is_k) ? hs * dk : (H + G) * dk + (hs - H - G) * dv;
+  TA* dst = row + col0;
+  if (!is_q) {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int g = is_k ? hs - H : hs - H - G;
+    dst = (is_k ? k_cache : v_cache) + (((size_t)(slot / page) * G + g) * page + (slot % page)) * width;
+  }
+  constexpr int STEP = PAIR ? 64 : 32;
+  float x0[kPrepPairs], x1[kPrepPairs];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kPrepPairs; ++i) {
+    const int d = (PAIR ? 2 * lane : lane) + STEP * i;
+    x0[i] = x1[i] = 0.f;
+    if (d < width) {
+      if (PAIR) {
+        const float2 v = ld_pair(row + col0 + d);
+        x0[i] = v.x;
+        x1[i] = v.y;
+        if (bias != nullptr) {
+          x0[i] += __bfloat162float(bias[col0 + d]);
+          x1[i] += __bfloat162float(bias[col0 + d + 1]);
+        }
+      } else {
+        x0[i] = as_f32(row[col0 + d]);
+        if (bias != nullptr) x0[i] += __bfloat162float(bias[col0 + d]);
+      }
+      ss = fmaf(x0[i], x0[i], fmaf(x1[i], x1[i], ss));
     }
+  }
+  const bf16* w = is_q ? qnorm_w : (is_k ? knorm_w : nullptr);
+  float mul = 1.0f;
+  if (is_q || is_k) {
     ss = warp_sum(ss);
-    float mul = w != nullptr ? 1.0f / sqrtf(ss / (float)dk + eps) : 1.0f;   // no weight = no head norm
+    if (w != nullptr) mul = 1.0f / sqrtf(ss / (float)dk + eps);            // no weight = no head norm
     if (is_q && temp_every > 0) {
       const int steps = (positions[t] + 1) / temp_every;
       mul *= 1.0f + temp_coef * logf((float)steps + 1.0f);
     }
-    TA* dst = row + col0;
-    if (!is_q) {
-      const int slot = slots[t];
-      if (slot < 0) return;
-      const int g = hs - H;
-      dst = k_cache + (((size_t)(slot / page) * G + g) * page + (slot % page)) * dk;
-    }
-    for (int d = lane; d < dk; d += 32) {
-      float v = as_f32(row[col0 + d]);
-      if (bias != nullptr) v += __bfloat162float(bias[col0 + d]);
-      const float wv = w != nullptr ? __bfloat162float(w[d]) : 1.0f;
-      as_store(dst + d, v * mul * wv);
-    }
-  } else {
-    const int g = hs - H - G;
-    const int col0 = (H + G) * dk + g * dv;
-    const int slot = slots[t];
-    if (slot < 0) return;
-    TA* dst = v_cache + (((size_t)(slot / page) * G + g) * page + (slot % page)) * dv;
-    for (int d = lane; d < dv; d += 32) {
-      float v = as_f32(row[col0 + d]);
-      if (bias != nullptr) v += __bfloat162float(bias[col0 + d]);
-      as_store(dst + d, v);
+  }
+#pragma unroll
+  for (int i = 0; i < kPrepPairs; ++i) {
+    const int d = (PAIR ? 2 * lane : lane) + STEP * i;
+    if (d < width) {
+      const float w0 = w != nullptr ? __bfloat162float(w[d]) : 1.0f;
+      if (PAIR) {
+        const float w1 = w != nullptr ? __bfloat162float(w[d + 1]) : 1.0f;
+        st_pair(dst + d, x0[i] * mul * w0, x1[i] * mul * w1);
+      } else {
+        as_store(dst + d, x0[i] * mul * w0);
+      }
     }
   }
 }
@@ -294,16 +324,22 @@ extern "C" int b200_attn_prep(void* proj, int f32, int64_t ld, const void* bias,
                               float temp_coef, int temp_every, void* stream) {
   B200_REQUIRE(T >= 0 && H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && page > 0, "attn_prep: bad shape");
   if (T == 0) return B200_OK;
-  dim3 grid(T, has_kv ? H + 2 * G : H);
+  const int n_slots = has_kv ? H + 2 * G : H;
+  dim3 grid(T, (n_slots + kPrepWarps - 1) / kPrepWarps);
   cudaStream_t s = (cudaStream_t)stream;
-  if (f32)
-    attn_prep_kernel<float><<<grid, 32, 0, s>>>((float*)proj, ld, (const bf16*)bias, (const bf16*)qnorm_w,
-                                                (const bf16*)knorm_w, positions, slots, (float*)k_cache,
-                                                (float*)v_cache, H, G, dk, dv, page, eps, temp_coef, temp_every);
-  else
-    attn_prep_kernel<bf16><<<grid, 32, 0, s>>>((bf16*)proj, ld, (const bf16*)bias, (const bf16*)qnorm_w,
-                                               (const bf16*)knorm_w, positions, slots, (bf16*)k_cache, (bf16*)v_cache,
-                                               H, G, dk, dv, page, eps, temp_coef, temp_every);
+  const int esz = f32 ? 4 : 2;
+  const bool pair = dk % 2 == 0 && dv % 2 == 0 && ld % 2 == 0 && (reinterpret_cast<uintptr_t>(proj) % (2 * esz)) == 0 &&
+                    (!has_kv || ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) % (2 * esz)) == 0);
+  B200_REQUIRE(dk <= (pair ? 64 : 32) * kPrepPairs && dv <= (pair ? 64 : 32) * kPrepPairs,
+               "attn_prep: head widths %d / %d exceed %d", dk, dv, (pair ? 64 : 32) * kPrepPairs);
+#define B200_PREP(TA, P)                                                                                         \
+  attn_prep_kernel<TA, P><<<grid, kPrepWarps * 32, 0, s>>>((TA*)proj, ld, (const bf16*)bias, (const bf16*)qnorm_w, \
+                                                           (const bf16*)knorm_w, positions, slots, (TA*)k_cache,  \
+                                                           (TA*)v_cache, H, G, dk, dv, page, n_slots, eps,        \
+                                                           temp_coef, temp_every)
+  if (f32) { if (pair) B200_PREP(float, true); else B200_PREP(float, false); }
+  else { if (pair) B200_PREP(bf16, true); else B200_PREP(bf16, false); }
+#undef B200_PREP
   return b200_check_launch("b200_attn_prep");
 }
 

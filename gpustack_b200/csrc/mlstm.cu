@@ -10,13 +10,14 @@
 //
 // `mlstm_scan` runs a sequence's new tokens in order (a prompt portion, or the single token of a
 // decode step: the same launch serves mixed batches).  grid (sequences, heads, ceil(dv / 32)): a CTA
-// owns 32 value columns of one head's state; warp r of its 8 warps holds the key rows r, r + 8, ...
-// in registers.  Tokens are staged 16 at a time in shared memory; each token costs one block
-// barrier (partial S^T q and n.q sums of the 8 warps through a double-buffered exchange).  The
-// normaliser n and the stabiliser m are kept once per column slice, so CTAs of one head never
-// read what another one writes.  State of slot s: S [slots][H][dk][dv], n [slots][H][Z][dk],
-// m [slots][H][Z], Z = ceil(dv / 32).  A sequence whose context is empty starts from zero,
-// whatever the slot held before.
+// owns 32 value columns of one head's state, each of its 8 warps 4 of them; lane r of a warp holds the
+// key rows r, r + 32, ... of those columns in registers.  Tokens are staged 16 at a time in shared
+// memory; within a chunk the warps run on their own (S^T q and n.q are warp-shuffle reductions: no
+// block barrier per token).  The normaliser n and the stabiliser m are kept once per column slice, so
+// CTAs of one head never read what another one writes.  State of slot s, laid out so that a warp's
+// loads and stores are contiguous: S [slots][H][dv][dk] (key index fastest), n [slots][H][Z][dk],
+// m [slots][H][Z], Z = ceil(dv / 32).  A sequence whose context is empty starts from zero, whatever
+// the slot held before.
 //
 // `mlstm_out` then divides every head's o_t by its root mean square, multiplies by the norm
 // weight and the sigmoid output gate, and rounds to the activation type.
@@ -31,13 +32,14 @@ __device__ __forceinline__ float ml_f32(bf16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ void ml_store(float* p, float v) { *p = v; }
 __device__ __forceinline__ void ml_store(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-constexpr int kScanWarps = 8, kScanCols = 32, kScanTok = 16;
+constexpr int kScanWarps = 8, kScanColsPerWarp = 4, kScanCols = kScanWarps * kScanColsPerWarp, kScanTok = 16;
 
 __device__ __forceinline__ float log_sigmoid(float x) {
   // -softplus(-x), stable on both sides
   return x < 0.f ? x - log1pf(expf(x)) : -log1pf(expf(-x));
 }
 
+// EPT = key rows per lane = ceil(dk / 32)
 template <typename TA, int EPT>
 __global__ void __launch_bounds__(kScanWarps * 32)
 mlstm_scan_kernel(const TA* __restrict__ proj, int64_t ld, int q_col, int k_col, int v_col,
@@ -50,44 +52,43 @@ mlstm_scan_kernel(const TA* __restrict__ proj, int64_t ld, int q_col, int k_col,
   float* ks = qs + kScanTok * dk;                     // [16][dk]
   float* vs = ks + kScanTok * dk;                     // [16][32]
   float* gs = vs + kScanTok * kScanCols;              // [16][2]  (i, f) log gates
-  float* red = gs + kScanTok * 2;                     // [2][8][33]
   const int s = blockIdx.x, h = blockIdx.y, z = blockIdx.z, Z = gridDim.z;
   const int slot = state_slots[s];
   if (slot < 0) return;
   const int t0 = cu_seq[s], t1 = cu_seq[s + 1];
   if (t1 <= t0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int col = z * kScanCols + lane;
-  const bool col_ok = col < dv;
-  float* Sp = S_state + ((size_t)slot * H + h) * dk * dv;
+  const int c0 = z * kScanCols + warp * kScanColsPerWarp;          // this warp's first column
+  float* Sp = S_state + ((size_t)slot * H + h) * dv * dk;
   float* np = n_state + (((size_t)slot * H + h) * Z + z) * dk;
   float* mp = m_state + ((size_t)slot * H + h) * Z + z;
-  float S[EPT], nn[EPT], m = 0.f;
+  float S[EPT][kScanColsPerWarp], nn[EPT], m = 0.f;
   const bool fresh = ctx_lens[s] == 0;
 #pragma unroll
   for (int j = 0; j < EPT; ++j) {
-    const int row = warp + kScanWarps * j;
-    S[j] = (!fresh && row < dk && col_ok) ? Sp[(size_t)row * dv + col] : 0.f;
+    const int row = lane + 32 * j;
+#pragma unroll
+    for (int c = 0; c < kScanColsPerWarp; ++c)
+      S[j][c] = (!fresh && row < dk && c0 + c < dv) ? Sp[(size_t)(c0 + c) * dk + row] : 0.f;
     nn[j] = (!fresh && row < dk) ? np[row] : 0.f;
   }
   if (!fresh) m = *mp;
   const float bi = __bfloat162float(gate_bias[h]), bfg = __bfloat162float(gate_bias[H + h]);
-  int buf = 0;
-  for (int c0 = t0; c0 < t1; c0 += kScanTok) {
-    const int nt = min(kScanTok, t1 - c0);
-    __syncthreads();                                  // the previous chunk is fully consumed
+  for (int ch = t0; ch < t1; ch += kScanTok) {
+    const int nt = min(kScanTok, t1 - ch);
+    __syncthreads();                                  // every warp is done with the previous chunk
     for (int i = threadIdx.x; i < nt * dk; i += blockDim.x) {
       const int tt = i / dk, d = i - tt * dk;
-      const TA* row = proj + (size_t)(c0 + tt) * ld;
+      const TA* row = proj + (size_t)(ch + tt) * ld;
       qs[i] = ml_f32(row[q_col + h * dk + d]) * qscale;
       ks[i] = ml_f32(row[k_col + h * dk + d]);
     }
     for (int i = threadIdx.x; i < nt * kScanCols; i += blockDim.x) {
       const int tt = i / kScanCols, c = z * kScanCols + (i % kScanCols);
-      vs[i] = c < dv ? ml_f32(proj[(size_t)(c0 + tt) * ld + v_col + h * dv + c]) : 0.f;
+      vs[i] = c < dv ? ml_f32(proj[(size_t)(ch + tt) * ld + v_col + h * dv + c]) : 0.f;
     }
     if (threadIdx.x < nt) {
-      const float* gr = gates + (size_t)(c0 + threadIdx.x) * 2 * H;
+      const float* gr = gates + (size_t)(ch + threadIdx.x) * 2 * H;
       const float ai = gr[h] + bi, af = gr[H + h] + bfg;
       gs[threadIdx.x * 2] = cap * tanhf(ai / cap);
       gs[threadIdx.x * 2 + 1] = log_sigmoid(cap * tanhf(af / cap));
@@ -98,65 +99,83 @@ mlstm_scan_kernel(const TA* __restrict__ proj, int64_t ld, int q_col, int k_col,
       const float m_new = fmaxf(fg + m, ig);
       const float a = expf(fg + m - m_new), b = expf(ig - m_new);
       m = m_new;
-      const float bv = b * vs[tt * kScanCols + lane];
-      float num = 0.f, nq = 0.f;
+      float v[kScanColsPerWarp], num[kScanColsPerWarp], nq = 0.f;
+#pragma unroll
+      for (int c = 0; c < kScanColsPerWarp; ++c) {
+        v[c] = vs[tt * kScanCols + warp * kScanColsPerWarp + c];
+        num[c] = 0.f;
+      }
 #pragma unroll
       for (int j = 0; j < EPT; ++j) {
-        const int row = warp + kScanWarps * j;
+        const int row = lane + 32 * j;
         if (row < dk) {
           const float kk = ks[tt * dk + row], qq = qs[tt * dk + row];
-          S[j] = fmaf(a, S[j], kk * bv);
-          nn[j] = fmaf(a, nn[j], b * kk);
-          num = fmaf(S[j], qq, num);
+          const float bk = b * kk;
+          nn[j] = fmaf(a, nn[j], bk);
           nq = fmaf(nn[j], qq, nq);
-        }
-      }
-      float* rb = red + buf * (kScanWarps * 33);
-      rb[warp * 33 + lane] = num;
-      if (lane == 0) rb[warp * 33 + 32] = nq;
-      __syncthreads();
-      if (warp == 0) {
-        float tn = 0.f, tq = 0.f;
 #pragma unroll
-        for (int w = 0; w < kScanWarps; ++w) {
-          tn += rb[w * 33 + lane];
-          tq += rb[w * 33 + 32];
+          for (int c = 0; c < kScanColsPerWarp; ++c) {
+            S[j][c] = fmaf(a, S[j][c], bk * v[c]);
+            num[c] = fmaf(S[j][c], qq, num[c]);
+          }
         }
-        const float den = fmaxf(fabsf(tq), expf(-m)) + 1e-6f;
-        if (col_ok) o_raw[(size_t)(c0 + tt) * H * dv + h * dv + col] = tn / den;
       }
-      buf ^= 1;
+      nq = warp_sum(nq);
+#pragma unroll
+      for (int c = 0; c < kScanColsPerWarp; ++c) num[c] = warp_sum(num[c]);
+      const float den = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
+      if (lane < kScanColsPerWarp && c0 + lane < dv) {
+        float mine = num[0];
+#pragma unroll
+        for (int c = 1; c < kScanColsPerWarp; ++c) mine = lane == c ? num[c] : mine;
+        o_raw[(size_t)(ch + tt) * H * dv + h * dv + c0 + lane] = mine / den;
+      }
     }
   }
 #pragma unroll
   for (int j = 0; j < EPT; ++j) {
-    const int row = warp + kScanWarps * j;
+    const int row = lane + 32 * j;
     if (row < dk) {
-      if (col_ok) Sp[(size_t)row * dv + col] = S[j];
-      if (lane == 0) np[row] = nn[j];
+#pragma unroll
+      for (int c = 0; c < kScanColsPerWarp; ++c)
+        if (c0 + c < dv) Sp[(size_t)(c0 + c) * dk + row] = S[j][c];
+      if (warp == 0) np[row] = nn[j];
     }
   }
   if (threadIdx.x == 0) *mp = m;
 }
 
-// grid (T, H), one warp: o / rms(o) * w * sigmoid(gate)
+// one warp per (token, head), 8 warps per CTA: o / rms(o) * w * sigmoid(gate); the head is read once
+constexpr int kOutWarps = 8, kOutPer = 8;   // value width <= 256
 template <typename TA>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(kOutWarps * 32)
 mlstm_out_kernel(const float* __restrict__ o_raw, const TA* __restrict__ proj, int64_t ld, int gate_col,
-                 const bf16* __restrict__ norm_w, TA* out, int64_t ldo, int H, int dv, float eps) {
-  const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+                 const bf16* __restrict__ norm_w, TA* out, int64_t ldo, int T, int H, int dv, float eps) {
+  const int idx = blockIdx.x * kOutWarps + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (idx >= T * H) return;
+  const int t = idx / H, h = idx - t * H;
   const float* o = o_raw + (size_t)t * H * dv + h * dv;
+  float x[kOutPer];
   float ss = 0.f;
-  for (int d = lane; d < dv; d += 32) ss = fmaf(o[d], o[d], ss);
+#pragma unroll
+  for (int i = 0; i < kOutPer; ++i) {
+    const int d = lane + 32 * i;
+    x[i] = d < dv ? o[d] : 0.f;
+    ss = fmaf(x[i], x[i], ss);
+  }
   ss = warp_sum(ss);
   const float r = 1.0f / sqrtf(ss / (float)dv + eps);
-  for (int d = lane; d < dv; d += 32) {
-    float v = o[d] * r * __bfloat162float(norm_w[h * dv + d]);
-    if (gate_col >= 0) {
-      const float gv = ml_f32(proj[(size_t)t * ld + gate_col + h * dv + d]);
-      v *= 1.0f / (1.0f + expf(-gv));
+#pragma unroll
+  for (int i = 0; i < kOutPer; ++i) {
+    const int d = lane + 32 * i;
+    if (d < dv) {
+      float v = x[i] * r * __bfloat162float(norm_w[h * dv + d]);
+      if (gate_col >= 0) {
+        const float gv = ml_f32(proj[(size_t)t * ld + gate_col + h * dv + d]);
+        v *= 1.0f / (1.0f + expf(-gv));
+      }
+      ml_store(out + (size_t)t * ldo + h * dv + d, v);
     }
-    ml_store(out + (size_t)t * ldo + h * dv + d, v);
   }
 }
 
@@ -167,9 +186,8 @@ static int launch_scan(const void* proj, int64_t ld, int q_col, int k_col, int v
                        int n_seq, int H, int dk, int dv, float cap, float qscale, cudaStream_t s) {
   const int Z = (dv + kScanCols - 1) / kScanCols;
   dim3 grid(n_seq, H, Z);
-  const size_t smem = sizeof(float) * ((size_t)2 * kScanTok * dk + kScanTok * kScanCols + kScanTok * 2 +
-                                       2 * kScanWarps * 33);
-  const int ept = (dk + kScanWarps - 1) / kScanWarps;
+  const size_t smem = sizeof(float) * ((size_t)2 * kScanTok * dk + kScanTok * kScanCols + kScanTok * 2);
+  const int ept = (dk + 31) / 32;
 #define B200_SCAN(E)                                                                                              \
   do {                                                                                                            \
     if (smem > 48 * 1024)                                                                                         \
@@ -178,12 +196,12 @@ static int launch_scan(const void* proj, int64_t ld, int q_col, int k_col, int v
         (const TA*)proj, ld, q_col, k_col, v_col, gates, (const bf16*)gate_bias, cu_seq, ctx_lens, state_slots,  \
         S_state, n_state, m_state, o_raw, H, dk, dv, cap, qscale);                                                \
   } while (0)
-  if (ept <= 4) B200_SCAN(4);
+  if (ept <= 1) B200_SCAN(1);
+  else if (ept <= 2) B200_SCAN(2);
+  else if (ept <= 4) B200_SCAN(4);
   else if (ept <= 8) B200_SCAN(8);
-  else if (ept <= 16) B200_SCAN(16);
-  else if (ept <= 32) B200_SCAN(32);
   else {
-    b200_set_error("mlstm_scan: key width %d exceeds %d", dk, 32 * kScanWarps);
+    b200_set_error("mlstm_scan: key width %d exceeds 256", dk);
     return B200_ERR_UNSUPPORTED;
   }
 #undef B200_SCAN
@@ -215,15 +233,15 @@ extern "C" int b200_mlstm_scan(const void* proj, int f32, int64_t ld, int q_col,
 extern "C" int b200_mlstm_out(const float* o_raw, const void* proj, int f32, int64_t ld, int gate_col,
                               const void* norm_w, void* out, int64_t ldo, int T, int H, int dv, float eps,
                               void* stream) {
-  B200_REQUIRE(T >= 0 && H > 0 && dv > 0, "mlstm_out: bad shape");
+  B200_REQUIRE(T >= 0 && H > 0 && dv > 0 && dv <= 32 * kOutPer, "mlstm_out: bad shape (value width <= %d)", 32 * kOutPer);
   if (T == 0) return B200_OK;
   cudaStream_t s = (cudaStream_t)stream;
-  dim3 grid(T, H);
+  const int grid = (int)(((size_t)T * H + kOutWarps - 1) / kOutWarps);
   if (f32)
-    mlstm_out_kernel<float><<<grid, 32, 0, s>>>(o_raw, (const float*)proj, ld, gate_col, (const bf16*)norm_w,
-                                                (float*)out, ldo, H, dv, eps);
+    mlstm_out_kernel<float><<<grid, kOutWarps * 32, 0, s>>>(o_raw, (const float*)proj, ld, gate_col, (const bf16*)norm_w,
+                                                            (float*)out, ldo, T, H, dv, eps);
   else
-    mlstm_out_kernel<bf16><<<grid, 32, 0, s>>>(o_raw, (const bf16*)proj, ld, gate_col, (const bf16*)norm_w, (bf16*)out,
-                                               ldo, H, dv, eps);
+    mlstm_out_kernel<bf16><<<grid, kOutWarps * 32, 0, s>>>(o_raw, (const bf16*)proj, ld, gate_col, (const bf16*)norm_w,
+                                                           (bf16*)out, ldo, T, H, dv, eps);
   return b200_check_launch("b200_mlstm_out");
 }

@@ -237,7 +237,7 @@ def _kernel_numbers(size, T, B, ctx, log):
     gb = rnd(2 * Hm)
     Z = ops.mlstm_state_slices(hd)
     nslot = max(S, B)
-    Sst = torch.zeros(nslot, Hm, hd, hd, device=dev)
+    Sst = torch.zeros(nslot, Hm, hd, hd, device=dev)      # [slots, H, dv, dk]
     nst, mst = torch.zeros(nslot, Hm, Z, hd, device=dev), torch.zeros(nslot, Hm, Z, device=dev)
     o_raw = torch.empty(T, Hm * hd, device=dev)
     t_scan = _time(lambda: ops.mlstm_scan(pm, 0, Hm * hd, 2 * Hm * hd, gates, gb, cu, ctx0, i32(np.arange(S)), Sst, nst, mst, o_raw,

@@ -104,7 +104,7 @@ class LayerListRunner(ModelRunner):
 
     def init_state(self, num_slots: int) -> None:
         """fp32 recurrent state of every mlstm layer for `num_slots` sequences (kv_cache.StateSlotPool hands
-        the slots out): S [slots, H, dk, dv], and per 32-column slice of dv the normaliser n [slots, H, Z, dk]
+        the slots out): S [slots, H, dv, dk] (key index fastest), and per 32-column slice of dv the normaliser n [slots, H, Z, dk]
         and the stabiliser m [slots, H, Z]."""
         self.num_state_slots = num_slots
         for l, layer in enumerate(self.mcfg.layers):
@@ -113,7 +113,7 @@ class LayerListRunner(ModelRunner):
                 continue
             z = ops.mlstm_state_slices(m.vdim)
             f = lambda *s: torch.zeros(*s, dtype=torch.float32, device=self.device)   # noqa: E731
-            self.state[l] = (f(num_slots, m.heads, m.dim, m.vdim), f(num_slots, m.heads, z, m.dim), f(num_slots, m.heads, z))
+            self.state[l] = (f(num_slots, m.heads, m.vdim, m.dim), f(num_slots, m.heads, z, m.dim), f(num_slots, m.heads, z))
 
     def init_host_kv(self, slots: int) -> None:
         self.host_slots = 0          # no prefix reuse with recurrent state: nothing to keep on the host

@@ -298,7 +298,7 @@ int b200_gemm_bf16_relu2(const void* X, const void* W, void* Y, int M, int N, in
 int b200_mlstm_state_slices(int dv);
 /* Stabilised matrix-memory recurrence over each sequence's new rows [cu_seq[s], cu_seq[s+1]); gates
  * [T][2H] fp32 raw (input | forget) projections, gate_bias [2H] bf16; state of slot state_slots[s]
- * (S [slots][H][dk][dv], n [slots][H][Z][dk], m [slots][H][Z], fp32) is read unless ctx_lens[s] == 0
+ * (S [slots][H][dv][dk], n [slots][H][Z][dk], m [slots][H][Z], fp32) is read unless ctx_lens[s] == 0
  * and written back; o_raw [T][H*dv] fp32.  Negative slot: the sequence is skipped. */
 int b200_mlstm_scan(const void* proj, int f32, int64_t ld, int q_col, int k_col, int v_col,
                     const float* gates, const void* gate_bias, const int32_t* cu_seq,

@@ -274,7 +274,7 @@ def test_mlstm_scan_portions_and_slots(dtype, H, dk, dv):
     gates = torch.cat([gi, gf], dim=1).float().cuda().contiguous()
     slots = 3
     Z = ops.mlstm_state_slices(dv)
-    S = torch.full((slots, H, dk, dv), 5.0, device="cuda")          # junk: a fresh sequence must not read it
+    S = torch.full((slots, H, dv, dk), 5.0, device="cuda")          # junk: a fresh sequence must not read it
     n = torch.full((slots, H, Z, dk), -5.0, device="cuda")
     m = torch.full((slots, H, Z), 11.0, device="cuda")
     o = torch.zeros(T, H * dv, device="cuda")
