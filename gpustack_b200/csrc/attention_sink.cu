@@ -111,6 +111,70 @@ attn_prep_kernel(TA* proj, int64_t ld, const bf16* __restrict__ bias, const bf16
   }
 }
 
+// The same step with 16-byte loads and stores, for widths that are multiples of 16 bytes (every real head
+// size): LPH lanes share a head (LPH = a power of two >= width / VEC), a warp covers 32 / LPH head slots of one
+// token, each lane moves one 16-byte piece of the row, of the bias and of the norm weight.
+template <typename TA>
+__global__ void __launch_bounds__(kPrepWarps * 32)
+attn_prep_vec_kernel(TA* proj, int64_t ld, const bf16* __restrict__ bias, const bf16* __restrict__ qnorm_w,
+                     const bf16* __restrict__ knorm_w, const int32_t* __restrict__ positions,
+                     const int32_t* __restrict__ slots, TA* k_cache, TA* v_cache, int H, int G, int dk, int dv, int page,
+                     int n_slots, int lph, float eps, float temp_coef, int temp_every) {
+  constexpr int VEC = 16 / (int)sizeof(TA);
+  const int t = blockIdx.x, lane = threadIdx.x & 31, per_warp = 32 / lph;
+  const int hs = (blockIdx.y * kPrepWarps + (threadIdx.x >> 5)) * per_warp + lane / lph;
+  const int li = lane % lph;
+  const bool live = hs < n_slots;
+  const bool is_q = live && hs < H, is_k = live && !is_q && hs < H + G;
+  const int width = (is_q || is_k) ? dk : dv;
+  const int col0 = !live ? 0 : ((is_q || is_k) ? hs * dk : (H + G) * dk + (hs - H - G) * dv);
+  const int d = li * VEC;
+  const bool act = live && d < width;
+  TA* row = proj + (size_t)t * ld;
+  float x[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) x[i] = 0.f;
+  if (act) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(row + col0 + d);
+    const TA* rv = reinterpret_cast<const TA*>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) x[i] = as_f32(rv[i]);
+    if (bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) x[i] += __bfloat162float(bias[col0 + d + i]);
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) ss = fmaf(x[i], x[i], ss);
+  for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // all lanes take part
+  if (!act) return;
+  const bf16* w = is_q ? qnorm_w : (is_k ? knorm_w : nullptr);
+  float mul = 1.0f;
+  if (is_q || is_k) {
+    if (w != nullptr) mul = 1.0f / sqrtf(ss / (float)dk + eps);
+    if (is_q && temp_every > 0) {
+      const int steps = (positions[t] + 1) / temp_every;
+      mul *= 1.0f + temp_coef * logf((float)steps + 1.0f);
+    }
+  }
+  TA* dst = row + col0;
+  if (!is_q) {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int g = is_k ? hs - H : hs - H - G;
+    dst = (is_k ? k_cache : v_cache) + (((size_t)(slot / page) * G + g) * page + (slot % page)) * width;
+  }
+  uint4 outv;
+  TA* ov = reinterpret_cast<TA*>(&outv);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const float wv = w != nullptr ? __bfloat162float(w[d + i]) : 1.0f;
+    as_store(ov + i, x[i] * mul * wv);
+  }
+  *reinterpret_cast<uint4*>(dst + d) = outv;
+}
+
 // -------------------------------------------------------------------------------------- prefill
 constexpr int kPfRows = 16, kPfKeys = 32, kPfWarps = 4, kPfRowsPerWarp = kPfRows / kPfWarps;
 
@@ -330,6 +394,27 @@ extern "C" int b200_attn_prep(void* proj, int f32, int64_t ld, const void* bias,
   const int esz = f32 ? 4 : 2;
   const bool pair = dk % 2 == 0 && dv % 2 == 0 && ld % 2 == 0 && (reinterpret_cast<uintptr_t>(proj) % (2 * esz)) == 0 &&
                     (!has_kv || ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) % (2 * esz)) == 0);
+  {
+    // 16-byte path: widths, offsets and pitches that are multiples of 16 bytes, at most 32 pieces per head
+    const int vec = 16 / esz, wmax = dk > dv ? dk : dv;
+    const bool al = ((reinterpret_cast<uintptr_t>(proj) | (has_kv ? reinterpret_cast<uintptr_t>(k_cache) |
+                                                            reinterpret_cast<uintptr_t>(v_cache) : 0)) & 15) == 0;
+    if (al && dk % vec == 0 && dv % vec == 0 && ld % vec == 0 && wmax / vec <= 32) {
+      int lph = 1;
+      while (lph < wmax / vec) lph <<= 1;
+      const int per_block = kPrepWarps * (32 / lph);
+      dim3 vgrid(T, (n_slots + per_block - 1) / per_block);
+      if (f32)
+        attn_prep_vec_kernel<float><<<vgrid, kPrepWarps * 32, 0, s>>>(
+            (float*)proj, ld, (const bf16*)bias, (const bf16*)qnorm_w, (const bf16*)knorm_w, positions, slots,
+            (float*)k_cache, (float*)v_cache, H, G, dk, dv, page, n_slots, lph, eps, temp_coef, temp_every);
+      else
+        attn_prep_vec_kernel<bf16><<<vgrid, kPrepWarps * 32, 0, s>>>(
+            (bf16*)proj, ld, (const bf16*)bias, (const bf16*)qnorm_w, (const bf16*)knorm_w, positions, slots,
+            (bf16*)k_cache, (bf16*)v_cache, H, G, dk, dv, page, n_slots, lph, eps, temp_coef, temp_every);
+      return b200_check_launch("b200_attn_prep");
+    }
+  }
   B200_REQUIRE(dk <= (pair ? 64 : 32) * kPrepPairs && dv <= (pair ? 64 : 32) * kPrepPairs,
                "attn_prep: head widths %d / %d exceed %d", dk, dv, (pair ? 64 : 32) * kPrepPairs);
 #define B200_PREP(TA, P)                                                                                         \

@@ -74,6 +74,49 @@ mlstm_scan_kernel(const TA* __restrict__ proj, int64_t ld, int q_col, int k_col,
   }
   if (!fresh) m = *mp;
   const float bi = __bfloat162float(gate_bias[h]), bfg = __bfloat162float(gate_bias[H + h]);
+  if (t1 - t0 == 1) {
+    // a decode row: no staging and no barrier -- every lane fetches its own key / query elements, so the state
+    // and the inputs are in flight together and the CTA's life is one memory round trip
+    const TA* row = proj + (size_t)t0 * ld;
+    float kk[EPT], qq[EPT], v[kScanColsPerWarp];
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+      const int r = lane + 32 * j;
+      kk[j] = r < dk ? ml_f32(row[k_col + h * dk + r]) : 0.f;
+      qq[j] = r < dk ? ml_f32(row[q_col + h * dk + r]) * qscale : 0.f;
+    }
+#pragma unroll
+    for (int c = 0; c < kScanColsPerWarp; ++c) v[c] = c0 + c < dv ? ml_f32(row[v_col + h * dv + c0 + c]) : 0.f;
+    const float* gr = gates + (size_t)t0 * 2 * H;
+    const float ig = cap * tanhf((gr[h] + bi) / cap), fg = log_sigmoid(cap * tanhf((gr[H + h] + bfg) / cap));
+    const float m_new = fmaxf(fg + m, ig);
+    const float a = expf(fg + m - m_new), b = expf(ig - m_new);
+    m = m_new;
+    float num[kScanColsPerWarp], nq = 0.f;
+#pragma unroll
+    for (int c = 0; c < kScanColsPerWarp; ++c) num[c] = 0.f;
+#pragma unroll
+    for (int j = 0; j < EPT; ++j) {
+      const float bk = b * kk[j];
+      nn[j] = fmaf(a, nn[j], bk);
+      nq = fmaf(nn[j], qq[j], nq);
+#pragma unroll
+      for (int c = 0; c < kScanColsPerWarp; ++c) {
+        S[j][c] = fmaf(a, S[j][c], bk * v[c]);
+        num[c] = fmaf(S[j][c], qq[j], num[c]);
+      }
+    }
+    nq = warp_sum(nq);
+#pragma unroll
+    for (int c = 0; c < kScanColsPerWarp; ++c) num[c] = warp_sum(num[c]);
+    const float den = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
+    if (lane < kScanColsPerWarp && c0 + lane < dv) {
+      float mine = num[0];
+#pragma unroll
+      for (int c = 1; c < kScanColsPerWarp; ++c) mine = lane == c ? num[c] : mine;
+      o_raw[(size_t)t0 * H * dv + h * dv + c0 + lane] = mine / den;
+    }
+  } else
   for (int ch = t0; ch < t1; ch += kScanTok) {
     const int nt = min(kScanTok, t1 - ch);
     __syncthreads();                                  // every warp is done with the previous chunk
@@ -143,6 +186,200 @@ mlstm_scan_kernel(const TA* __restrict__ proj, int64_t ld, int q_col, int k_col,
     }
   }
   if (threadIdx.x == 0) *mp = m;
+}
+
+// ------------------------------------------------------------------------------------- chunk form
+// The same recurrence for prompt portions, 16 tokens at a time, without a serial dependency between the
+// tokens of a chunk.  With the state (S_0, n_0, m_0) at the chunk's start, F_t = f_1 + ... + f_t and the
+// stabilisers m_t of the serial form (a 16-step scalar chain):
+//     S_t^T q_t = e^{F_t + m_0 - m_t} S_0^T q_t + sum_{s<=t} e^{F_t - F_s + i_s - m_t} (k_s . q_t) v_s
+//     n_t . q_t = e^{F_t + m_0 - m_t} n_0 . q_t + sum_{s<=t} e^{F_t - F_s + i_s - m_t} (k_s . q_t)
+//     S_L       = e^{F_L + m_0 - m_L} S_0       + sum_s     e^{F_L - F_s + i_s - m_L} k_s v_s^T
+// Every exponent is <= 0 by the definition of m.  All products and sums are fp32 FMAs; only the grouping
+// of the sums differs from the serial form.  grid (sequences, heads, ceil(dv / 32)), 512 threads; the
+// CTA's 32 columns of S live in shared memory for the whole portion.
+constexpr int kChunkTok = 16, kChunkThreads = 512, kChunkPre = 8;   // 16 * 256 / 512
+
+template <typename TA>
+__global__ void __launch_bounds__(kChunkThreads)
+mlstm_chunk_kernel(const TA* __restrict__ proj, int64_t ld, int q_col, int k_col, int v_col,
+                   const float* __restrict__ gates, const bf16* __restrict__ gate_bias,
+                   const int32_t* __restrict__ cu_seq, const int32_t* __restrict__ ctx_lens,
+                   const int32_t* __restrict__ state_slots, float* S_state, float* n_state, float* m_state,
+                   float* __restrict__ o_raw, int H, int dk, int dv, float cap, float qscale) {
+  extern __shared__ float smem[];
+  const int dkp = dk + 1;
+  float* Ssm = smem;                                  // [dk][33]
+  float* qs = Ssm + dk * 33;                          // [16][dk + 1]
+  float* ks = qs + kChunkTok * dkp;                   // [16][dk + 1]
+  float* vs = ks + kChunkTok * dkp;                   // [16][32]
+  float* A = vs + kChunkTok * 32;                     // [16][17]   k_s . q_t
+  float* nsm = A + kChunkTok * 17;                    // [dk]
+  float* ig = nsm + dk;                               // [16] log input gates
+  float* fg = ig + kChunkTok;                         // [16] log forget gates
+  float* Fc = fg + kChunkTok;                         // [16] cumulative log forget gates
+  float* mm = Fc + kChunkTok;                         // [16] stabilisers
+  float* nq0 = mm + kChunkTok;                        // [16] n_0 . q_t
+  float* gl = nq0 + kChunkTok;                        // [16] weights of the state update
+  __shared__ float m_start;
+  const int s = blockIdx.x, h = blockIdx.y, z = blockIdx.z, Z = gridDim.z;
+  const int slot = state_slots[s];
+  if (slot < 0) return;
+  const int t0 = cu_seq[s], t1 = cu_seq[s + 1];
+  if (t1 <= t0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c0 = z * 32;
+  float* Sp = S_state + ((size_t)slot * H + h) * dv * dk;
+  float* np = n_state + (((size_t)slot * H + h) * Z + z) * dk;
+  float* mp = m_state + ((size_t)slot * H + h) * Z + z;
+  const bool fresh = ctx_lens[s] == 0;
+  for (int i = tid; i < dk * 32; i += kChunkThreads) {
+    const int c = i / dk, r = i - c * dk;             // r fastest: contiguous global reads
+    Ssm[r * 33 + c] = (!fresh && c0 + c < dv) ? Sp[(size_t)(c0 + c) * dk + r] : 0.f;
+  }
+  for (int r = tid; r < dk; r += kChunkThreads) nsm[r] = fresh ? 0.f : np[r];
+  if (tid == 0) m_start = fresh ? 0.f : *mp;
+  const float bi = __bfloat162float(gate_bias[h]), bfg = __bfloat162float(gate_bias[H + h]);
+  // The next chunk's inputs travel in registers while the current chunk is computed (kChunkPre elements of q
+  // and of k per thread: key width <= 256), so the loop never waits for a global load it has just issued.
+  TA rq[kChunkPre], rk[kChunkPre], rv;
+  float rgi = 0.f, rgf = 0.f;
+  auto fetch = [&](int ch, int nt) {
+#pragma unroll
+    for (int u = 0; u < kChunkPre; ++u) {
+      const int i = tid + u * kChunkThreads;
+      if (i < nt * dk) {
+        const int tt = i / dk, d = i - tt * dk;
+        const TA* row = proj + (size_t)(ch + tt) * ld;
+        rq[u] = row[q_col + h * dk + d];
+        rk[u] = row[k_col + h * dk + d];
+      }
+    }
+    {
+      const int tt = tid >> 5, c = c0 + (tid & 31);
+      if (tt < nt && c < dv) rv = proj[(size_t)(ch + tt) * ld + v_col + h * dv + c];
+    }
+    if (tid < nt) {
+      const float* gr = gates + (size_t)(ch + tid) * 2 * H;
+      rgi = gr[h];
+      rgf = gr[H + h];
+    }
+  };
+  fetch(t0, min(kChunkTok, t1 - t0));
+  for (int ch = t0; ch < t1; ch += kChunkTok) {
+    const int nt = min(kChunkTok, t1 - ch);
+    __syncthreads();                                  // state update of the previous chunk done, inputs free
+#pragma unroll
+    for (int u = 0; u < kChunkPre; ++u) {
+      const int i = tid + u * kChunkThreads;
+      if (i < nt * dk) {
+        const int tt = i / dk, d = i - tt * dk;
+        qs[tt * dkp + d] = ml_f32(rq[u]) * qscale;
+        ks[tt * dkp + d] = ml_f32(rk[u]);
+      }
+    }
+    {
+      const int tt = tid >> 5, c = c0 + (tid & 31);
+      vs[tid] = (tt < nt && c < dv) ? ml_f32(rv) : 0.f;
+    }
+    if (tid < nt) {
+      ig[tid] = cap * tanhf((rgi + bi) / cap);
+      fg[tid] = log_sigmoid(cap * tanhf((rgf + bfg) / cap));
+    }
+    if (ch + kChunkTok < t1) fetch(ch + kChunkTok, min(kChunkTok, t1 - ch - kChunkTok));
+    __syncthreads();
+    // (a) k_s . q_t for s <= t, n_0 . q_t, and -- one thread -- the serial scalars of the chunk
+    if (tid < 256) {
+      const int t = tid >> 4, sx = tid & 15;
+      if (t < nt && sx <= t) {
+        float acc = 0.f;
+        const float* kr = ks + sx * dkp;
+        const float* qr = qs + t * dkp;
+        for (int r = 0; r < dk; ++r) acc = fmaf(kr[r], qr[r], acc);
+        A[t * 17 + sx] = acc;
+      }
+    } else if (tid < 256 + kChunkTok) {
+      const int t = tid - 256;
+      if (t < nt) {
+        float acc = 0.f;
+        const float* qr = qs + t * dkp;
+        for (int r = 0; r < dk; ++r) acc = fmaf(nsm[r], qr[r], acc);
+        nq0[t] = acc;
+      }
+    } else if (tid == 288) {
+      float m = m_start, F = 0.f;
+      for (int t = 0; t < nt; ++t) {
+        m = fmaxf(fg[t] + m, ig[t]);
+        F += fg[t];
+        mm[t] = m;
+        Fc[t] = F;
+      }
+      const float mL = m, FL = F;
+      for (int t = 0; t < nt; ++t) gl[t] = expf(FL - Fc[t] + ig[t] - mL);
+    }
+    __syncthreads();
+    // (b) outputs: thread = (token = warp, column = lane)
+    if (warp < nt) {
+      const int t = warp;
+      const float mt = mm[t], Ft = Fc[t];
+      const float d0 = expf(Ft + m_start - mt);
+      float acc = 0.f;
+      const float* qr = qs + t * dkp;
+      for (int r = 0; r < dk; ++r) acc = fmaf(Ssm[r * 33 + lane], qr[r], acc);
+      float num = d0 * acc, nqv = d0 * nq0[t];
+      for (int sx = 0; sx <= t; ++sx) {
+        const float wa = expf(Ft - Fc[sx] + ig[sx] - mt) * A[t * 17 + sx];
+        num = fmaf(wa, vs[sx * 32 + lane], num);
+        nqv += wa;
+      }
+      const float den = fmaxf(fabsf(nqv), expf(-mt)) + 1e-6f;
+      if (c0 + lane < dv) o_raw[(size_t)(ch + t) * H * dv + h * dv + c0 + lane] = num / den;
+    }
+    __syncthreads();
+    // (c) state at the chunk's end
+    {
+      const float dL = expf(Fc[nt - 1] + m_start - mm[nt - 1]);
+      for (int r = warp; r < dk; r += kChunkThreads / 32) {
+        float acc = dL * Ssm[r * 33 + lane];
+        for (int sx = 0; sx < nt; ++sx) acc = fmaf(gl[sx] * ks[sx * dkp + r], vs[sx * 32 + lane], acc);
+        Ssm[r * 33 + lane] = acc;
+      }
+      for (int r = tid; r < dk; r += kChunkThreads) {
+        float acc = dL * nsm[r];
+        for (int sx = 0; sx < nt; ++sx) acc = fmaf(gl[sx], ks[sx * dkp + r], acc);
+        nsm[r] = acc;
+      }
+    }
+    __syncthreads();
+    if (tid == 0) m_start = mm[nt - 1];
+  }
+  __syncthreads();
+  for (int i = tid; i < dk * 32; i += kChunkThreads) {
+    const int c = i / dk, r = i - c * dk;
+    if (c0 + c < dv) Sp[(size_t)(c0 + c) * dk + r] = Ssm[r * 33 + c];
+  }
+  for (int r = tid; r < dk; r += kChunkThreads) np[r] = nsm[r];
+  if (tid == 0) *mp = m_start;
+}
+
+template <typename TA>
+static int launch_chunk(const void* proj, int64_t ld, int q_col, int k_col, int v_col, const float* gates,
+                        const void* gate_bias, const int32_t* cu_seq, const int32_t* ctx_lens,
+                        const int32_t* state_slots, float* S_state, float* n_state, float* m_state, float* o_raw,
+                        int n_seq, int H, int dk, int dv, float cap, float qscale, cudaStream_t s) {
+  dim3 grid(n_seq, H, (dv + 31) / 32);
+  const size_t smem = sizeof(float) * ((size_t)dk * 33 + 2 * kChunkTok * (dk + 1) + kChunkTok * 32 + kChunkTok * 17 + dk +
+                                       6 * kChunkTok);
+  if (smem > 200 * 1024 || dk > kChunkPre * kChunkThreads / kChunkTok) {
+    b200_set_error("mlstm_scan: key width %d exceeds %d", dk, kChunkPre * kChunkThreads / kChunkTok);
+    return B200_ERR_UNSUPPORTED;
+  }
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(mlstm_chunk_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  mlstm_chunk_kernel<TA><<<grid, kChunkThreads, smem, s>>>((const TA*)proj, ld, q_col, k_col, v_col, gates,
+                                                          (const bf16*)gate_bias, cu_seq, ctx_lens, state_slots, S_state,
+                                                          n_state, m_state, o_raw, H, dk, dv, cap, qscale);
+  return b200_check_launch("b200_mlstm_scan(chunk)");
 }
 
 // one warp per (token, head), 8 warps per CTA: o / rms(o) * w * sigmoid(gate); the head is read once
@@ -218,11 +455,18 @@ extern "C" int b200_mlstm_scan(const void* proj, int f32, int64_t ld, int q_col,
                                const float* gates, const void* gate_bias, const int32_t* cu_seq,
                                const int32_t* ctx_lens, const int32_t* state_slots, float* S_state, float* n_state,
                                float* m_state, float* o_raw, int n_seq, int H, int dk, int dv, float cap, float qscale,
-                               void* stream) {
+                               int max_len, void* stream) {
   B200_REQUIRE(n_seq >= 0 && H > 0 && dk > 0 && dv > 0 && cap > 0.f, "mlstm_scan: bad shape H=%d dk=%d dv=%d", H, dk,
                dv);
   if (n_seq == 0) return B200_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  if (max_len >= 4) {   // prompt portions: the chunk form; single rows and tiny portions: the serial form
+    if (f32)
+      return launch_chunk<float>(proj, ld, q_col, k_col, v_col, gates, gate_bias, cu_seq, ctx_lens, state_slots, S_state,
+                                 n_state, m_state, o_raw, n_seq, H, dk, dv, cap, qscale, s);
+    return launch_chunk<bf16>(proj, ld, q_col, k_col, v_col, gates, gate_bias, cu_seq, ctx_lens, state_slots, S_state,
+                              n_state, m_state, o_raw, n_seq, H, dk, dv, cap, qscale, s);
+  }
   if (f32)
     return launch_scan<float>(proj, ld, q_col, k_col, v_col, gates, gate_bias, cu_seq, ctx_lens, state_slots, S_state,
                               n_state, m_state, o_raw, n_seq, H, dk, dv, cap, qscale, s);

@@ -192,9 +192,10 @@ def _kernel_numbers(size, T, B, ctx, log):
     sink = rnd(H, dt=f32)
     out = torch.empty(T, H * hd, device=dev, dtype=bf)
     gate_col = (H + 2 * G) * hd
-    t_new = _time(lambda: ops.paged_attn_prefill_ex(proj, W, kc, vc, bt, cu, ctx0, i32(ts_), i32(tq_), out, H, G, hd, hd ** -0.5,
-                                                    sink=sink, gate=proj[:, gate_col:]), flush)
-    t_like = _time(lambda: ops.paged_attn_prefill(qkv, qkv.shape[1], kc, vc, bt, cu, ctx0, i32(ts_), i32(tq_), out, H, G, hd,
+    ts_d, tq_d, gate_v = i32(ts_), i32(tq_), proj[:, gate_col:]       # nothing but the launch inside the timed region
+    t_new = _time(lambda: ops.paged_attn_prefill_ex(proj, W, kc, vc, bt, cu, ctx0, ts_d, tq_d, out, H, G, hd, hd ** -0.5,
+                                                    sink=sink, gate=gate_v), flush)
+    t_like = _time(lambda: ops.paged_attn_prefill(qkv, qkv.shape[1], kc, vc, bt, cu, ctx0, ts_d, tq_d, out, H, G, hd,
                                                   hd ** -0.5), flush)
     fl = 4.0 * S * (L * L / 2) * H * hd
     t_pf_like = t_like
@@ -206,7 +207,8 @@ def _kernel_numbers(size, T, B, ctx, log):
     kcg, vcg = rnd(nblk, G, 16, dk), rnd(nblk, G, 16, dv)
     outg = torch.empty(T, H * dv, device=dev, dtype=bf)
     tsg, tqg = ops.build_prefill_tiles([L] * S, 16, [0] * S)
-    t_gen = _time(lambda: ops.attn_sink_prefill(projg, (H + G) * dk + G * dv, kcg, vcg, bt, cu, ctx0, i32(tsg), i32(tqg), sink, outg,
+    tsg, tqg = i32(tsg), i32(tqg)
+    t_gen = _time(lambda: ops.attn_sink_prefill(projg, (H + G) * dk + G * dv, kcg, vcg, bt, cu, ctx0, tsg, tqg, sink, outg,
                                                 H, G, dk, dv, dk ** -0.5), flush, iters=3, warm=1)
     flg = 2.0 * S * (L * L / 2) * H * (dk + dv)
     put("attn_sink_prefill generic", t_gen, flg, "paged_attn_prefill tc", t_pf_like, fl, "flops")
@@ -218,15 +220,17 @@ def _kernel_numbers(size, T, B, ctx, log):
     splits = ops.attn_decode_splits(B, G, ctx + 16)
     ws = ops.attn_decode_workspace(B, H, hd, splits, dev)
     outd = torch.empty(B, H * hd, device=dev, dtype=bf)
-    t_new = _time(lambda: ops.paged_attn_decode(proj[:B], W, kc, vc, btd, lens, outd, H, G, hd, hd ** -0.5, num_splits=splits,
-                                                workspace=ws, sink=sink, gate=proj[:B, gate_col:]), flush)
-    t_like = _time(lambda: ops.paged_attn_decode(qkv[:B], qkv.shape[1], kc, vc, btd, lens, outd, H, G, hd, hd ** -0.5,
+    pB, gB, qB = proj[:B], proj[:B, gate_col:], qkv[:B]
+    t_new = _time(lambda: ops.paged_attn_decode(pB, W, kc, vc, btd, lens, outd, H, G, hd, hd ** -0.5, num_splits=splits,
+                                                workspace=ws, sink=sink, gate=gB), flush)
+    t_like = _time(lambda: ops.paged_attn_decode(qB, qkv.shape[1], kc, vc, btd, lens, outd, H, G, hd, hd ** -0.5,
                                                  num_splits=splits, workspace=ws), flush)
     kvb = B * ctx * G * hd * 2 * 2.0
     t_dec_like = t_like
     put("attn_decode(sink,gate)", t_new, kvb, "paged_attn_decode", t_like, kvb, "bytes")
     outdg = torch.empty(B, H * dv, device=dev, dtype=bf)
-    t_gen = _time(lambda: ops.attn_sink_decode(projg[:B], (H + G) * dk + G * dv, kcg, vcg, btd, lens, sink, outdg, H, G, dk, dv,
+    pgB = projg[:B]
+    t_gen = _time(lambda: ops.attn_sink_decode(pgB, (H + G) * dk + G * dv, kcg, vcg, btd, lens, sink, outdg, H, G, dk, dv,
                                                dk ** -0.5), flush)
     put("attn_sink_decode generic", t_gen, B * ctx * G * (dk + dv) * 2.0, "paged_attn_decode", t_dec_like, kvb, "bytes")
 
@@ -240,12 +244,14 @@ def _kernel_numbers(size, T, B, ctx, log):
     Sst = torch.zeros(nslot, Hm, hd, hd, device=dev)      # [slots, H, dv, dk]
     nst, mst = torch.zeros(nslot, Hm, Z, hd, device=dev), torch.zeros(nslot, Hm, Z, device=dev)
     o_raw = torch.empty(T, Hm * hd, device=dev)
-    t_scan = _time(lambda: ops.mlstm_scan(pm, 0, Hm * hd, 2 * Hm * hd, gates, gb, cu, ctx0, i32(np.arange(S)), Sst, nst, mst, o_raw,
-                                          Hm, hd, hd, 15.0), flush, iters=3, warm=1)
+    slot_s, slot_b = i32(np.arange(S)), i32(np.arange(B))
+    t_scan = _time(lambda: ops.mlstm_scan(pm, 0, Hm * hd, 2 * Hm * hd, gates, gb, cu, ctx0, slot_s, Sst, nst, mst, o_raw,
+                                          Hm, hd, hd, 15.0, max_len=L), flush, iters=3, warm=1)
     put("mlstm_scan prefill", t_scan, 6.0 * T * Hm * hd * hd, "paged_attn_prefill tc", t_pf_like, fl, "flops")
     cud, ctxd = i32(np.arange(B + 1)), i32(np.full(B, ctx))
-    t_step = _time(lambda: ops.mlstm_scan(pm[:B], 0, Hm * hd, 2 * Hm * hd, gates[:B], gb, cud, ctxd, i32(np.arange(B)), Sst, nst, mst,
-                                          o_raw[:B], Hm, hd, hd, 15.0), flush)
+    pmB, gatesB, orB = pm[:B], gates[:B], o_raw[:B]
+    t_step = _time(lambda: ops.mlstm_scan(pmB, 0, Hm * hd, 2 * Hm * hd, gatesB, gb, cud, ctxd, slot_b, Sst, nst, mst,
+                                          orB, Hm, hd, hd, 15.0), flush)
     put("mlstm_scan decode", t_step, B * Hm * hd * hd * 8.0, "paged_attn_decode", t_dec_like, kvb, "bytes")
     mo = torch.empty(T, Hm * hd, device=dev, dtype=bf)
     nw = rnd(Hm * hd)

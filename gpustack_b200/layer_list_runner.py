@@ -185,7 +185,7 @@ class LayerListRunner(ModelRunner):
                 o_raw = self._view(self.o_raw, T, H * dv)
                 S, n, mm = self.state[l]
                 ops.mlstm_scan(proj, 0, H * dk, 2 * H * dk, gates, lw.gate_bias, cu_all, ctx_all, slots_all, S, n, mm,
-                               o_raw, H, dk, dv, m.gate_cap)
+                               o_raw, H, dk, dv, m.gate_cap, max_len=Tp if Tp else 1)
                 ops.mlstm_out(o_raw, proj, 2 * H * dk + H * dv, lw.out_norm, out, H, dv, eps)
                 self.stats["kernel_launches"] += 4
             ops.linear(out, lw.o, self.y[:T])

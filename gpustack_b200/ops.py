@@ -552,13 +552,14 @@ def mlstm_state_slices(dv: int) -> int:
 
 
 def mlstm_scan(proj, q_col, k_col, v_col, gates, gate_bias, cu_seq, ctx_lens, state_slots, S, n, m, o_raw, H, dk, dv,
-               cap: float):
-    """Runs every sequence's new rows through the matrix-memory recurrence (state slot in, state slot out)."""
+               cap: float, max_len: int = 1):
+    """Runs every sequence's new rows through the matrix-memory recurrence (state slot in, state slot out).
+    max_len: an upper bound of the new rows per sequence (prompt portions run in the chunk form)."""
     _cuda(proj, gates, gate_bias, cu_seq, ctx_lens, state_slots, S, n, m, o_raw)
     _req(gates, torch.float32, "gates"); _req(S, torch.float32, "S"); _req(o_raw, torch.float32, "o_raw")
     check(load().b200_mlstm_scan(_p(proj), _is_f32(proj), proj.stride(0), q_col, k_col, v_col, _p(gates), _p(gate_bias),
                                  _p(cu_seq), _p(ctx_lens), _p(state_slots), _p(S), _p(n), _p(m), _p(o_raw),
-                                 state_slots.shape[0], H, dk, dv, cap, dk ** -0.5, _stream()), "mlstm_scan")
+                                 state_slots.shape[0], H, dk, dv, cap, dk ** -0.5, int(max_len), _stream()), "mlstm_scan")
 
 
 def mlstm_out(o_raw, proj, gate_col, norm_w, out, H, dv, eps):

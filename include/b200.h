@@ -299,12 +299,13 @@ int b200_mlstm_state_slices(int dv);
 /* Stabilised matrix-memory recurrence over each sequence's new rows [cu_seq[s], cu_seq[s+1]); gates
  * [T][2H] fp32 raw (input | forget) projections, gate_bias [2H] bf16; state of slot state_slots[s]
  * (S [slots][H][dv][dk], n [slots][H][Z][dk], m [slots][H][Z], fp32) is read unless ctx_lens[s] == 0
- * and written back; o_raw [T][H*dv] fp32.  Negative slot: the sequence is skipped. */
+ * and written back; o_raw [T][H*dv] fp32.  Negative slot: the sequence is skipped.  max_len: an upper bound of
+ * the sequences' new rows (>= 4 selects the chunk form for prompt portions, else the serial form). */
 int b200_mlstm_scan(const void* proj, int f32, int64_t ld, int q_col, int k_col, int v_col,
                     const float* gates, const void* gate_bias, const int32_t* cu_seq,
                     const int32_t* ctx_lens, const int32_t* state_slots, float* S_state, float* n_state,
                     float* m_state, float* o_raw, int n_seq, int H, int dk, int dv, float cap, float qscale,
-                    void* stream);
+                    int max_len, void* stream);
 /* out = o_raw / rms_head(o_raw) * norm_w * sigmoid(gate). */
 int b200_mlstm_out(const float* o_raw, const void* proj, int f32, int64_t ld, int gate_col,
                    const void* norm_w, void* out, int64_t ldo, int T, int H, int dv, float eps,

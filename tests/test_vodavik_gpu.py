@@ -254,9 +254,10 @@ def test_attention_finds_one_far_key_and_respects_the_causal_edge(kernel):
         assert torch.allclose(out[-1].cpu(), v[far, 0], atol=1e-4), (kernel, far)
 
 
+@pytest.mark.parametrize("form", ["serial", "chunk"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,dk,dv", [(2, 10, 36), (1, 64, 64), (3, 44, 8), (2, 200, 40)])
-def test_mlstm_scan_portions_and_slots(dtype, H, dk, dv):
+def test_mlstm_scan_portions_and_slots(dtype, H, dk, dv, form):
     """The recurrence over portions of 1, 2 and many tokens with the state carried in a slot; a slot that held
     another sequence is reused; two sequences in one launch."""
     from gpustack_b200 import ops
@@ -282,14 +283,14 @@ def test_mlstm_scan_portions_and_slots(dtype, H, dk, dv):
     cuts = [0, 1, 3, 5, 22, 23, 40, T]
     for lo, hi in zip(cuts[:-1], cuts[1:]):
         ops.mlstm_scan(proj[lo:hi], 0, H * dk, 2 * H * dk, gates[lo:hi], bias.cuda(), i32([0, hi - lo]), i32([lo]), i32([1]),
-                       S, n, m, o[lo:hi], H, dk, dv, cap)
+                       S, n, m, o[lo:hi], H, dk, dv, cap, max_len=(hi - lo) if form == "chunk" else 1)
     tol = 3e-5 if dtype == torch.float32 else 2e-2
     assert _rel(o.cpu(), want.reshape(T, -1)) < tol
     assert float(S[0].min()) == 5.0 and float(S[2].max()) == 5.0       # other slots untouched
     # the same slot again from position 0, beside a second sequence that continues in slot 2 (skipped: slot -1)
     o2 = torch.zeros(T, H * dv, device="cuda")
     ops.mlstm_scan(proj, 0, H * dk, 2 * H * dk, gates, bias.cuda(), i32([0, 30, T]), i32([0, 30]), i32([1, -1]), S, n, m, o2,
-                   H, dk, dv, cap)
+                   H, dk, dv, cap, max_len=T if form == "chunk" else 1)
     assert _rel(o2[:30].cpu(), want.reshape(T, -1)[:30]) < tol
     assert float(o2[30:].abs().max()) == 0.0
 
