@@ -396,24 +396,6 @@ class LayerListConfig:
                 "norm": {"eps": self.norm_eps}, "postln_alpha": self.postln_alpha, "logit_scale": self.logit_scale}
 
 
-def vodavik_shape(width: int = 2048, layers: int = 4, heads: int = 16, kv_heads: int = 4, dim: int = 128,
-                  ff: int = 8192, vocab: int = 32000) -> LayerListConfig:
-    """A Vodavik model of real layer sizes for benchmarks (random weights): attention and mLSTM layers
-    alternate, every second attention layer reads the previous one's cache."""
-    specs = []
-    last_attn = None
-    for i in range(layers):
-        if i % 2 == 0:
-            share = last_attn if (last_attn is not None and (i // 2) % 2 == 1) else None
-            specs.append(LayerSpec(AttentionSpec(heads, kv_heads, dim, dim, dim ** -0.5, q_temp_coef=0.1, q_temp_every=1024,
-                                                 kv_from=share), MLPSpec("dense", ff)))
-            if share is None:
-                last_attn = i
-        else:
-            specs.append(LayerSpec(MLSTMSpec(max(1, heads // 2), dim, dim, 15.0), None))
-    return LayerListConfig("Vodavik", vocab, width, specs, norm_eps=1e-5, postln_alpha=2.0, logit_scale=1.0)
-
-
 # Named shapes used by tests and bench (random-init; there are no checkpoints offline).
 def llama3_8b() -> ModelConfig:
     return ModelConfig(vocab_size=128256, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32,

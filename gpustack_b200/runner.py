@@ -14,6 +14,7 @@ pinned int32 staging buffer copied host->device with a single cudaMemcpyAsync.
 """
 from __future__ import annotations
 
+import gc
 import math
 import os
 import time
@@ -484,6 +485,22 @@ class ModelRunner:
         if self.ecfg.enforce_eager:
             return
         self._prepare_capture()
+        # Python's cyclic collector must not run while a stream records: finalising an engine that an earlier
+        # caller dropped (its graphs' memory pool, pinned buffers) frees device memory, which invalidates the
+        # capture.  Collect once up front, then keep the collector off until the graphs are recorded.
+        gc_was_on = gc.isenabled()
+        gc.collect()
+        gc.disable()
+        try:
+            self._capture_buckets()
+        finally:
+            if gc_was_on:
+                gc.enable()
+        torch.cuda.synchronize()
+        self._buckets = sorted(self.graphs)
+        self.stats["kernel_launches"] = 0
+
+    def _capture_buckets(self) -> None:
         s = torch.cuda.Stream()
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
@@ -501,9 +518,6 @@ class ModelRunner:
                     self.graph_pool = g.pool()
                 self.graphs[B] = g
         torch.cuda.current_stream().wait_stream(s)
-        torch.cuda.synchronize()
-        self._buckets = sorted(self.graphs)
-        self.stats["kernel_launches"] = 0
 
     def decode(self, B: int, last_token: np.ndarray, num_computed: np.ndarray, block_table: np.ndarray,
                temps: Optional[np.ndarray] = None, seeds: Optional[np.ndarray] = None,
