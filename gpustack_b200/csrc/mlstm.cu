@@ -362,6 +362,227 @@ mlstm_chunk_kernel(const TA* __restrict__ proj, int64_t ld, int q_col, int k_col
   if (tid == 0) *mp = m_start;
 }
 
+// The chunk form again for key widths that are multiples of 4 (every real size), written for the instruction
+// count: 16-byte shared-memory loads of the token-major q / k rows (row pitch dk + 4), and register tiles so that
+// one loaded state element serves four tokens.  Phases per chunk (4 block barriers):
+//   P0  staged inputs -> shared memory; the next chunk's loads are issued
+//   P1  warps 0-7: A[t][s] = k_s . q_t (s <= t);  warps 8-11: n_0 . q_t;  warp 12: the serial scalars m_t, F_t
+//   P2  W[t][s] = e^{F_t - F_s + i_s - m_t} A[t][s];  partial S_0^T q_t: thread = (column, 4 tokens, a quarter of the rows)
+//   P3  o_t = (e^{F_t + m_0 - m_t} S_0^T q_t + sum_s W[t][s] v_s) / den_t            (thread = token, column)
+//   P4  S, n <- e^{F_L + m_0 - m_L} (S, n) + sum_s g_s k_s (v_s^T, 1)               (thread = column, 4-row groups)
+template <typename TA>
+__global__ void __launch_bounds__(kChunkThreads)
+mlstm_chunk4_kernel(const TA* __restrict__ proj, int64_t ld, int q_col, int k_col, int v_col,
+                    const float* __restrict__ gates, const bf16* __restrict__ gate_bias,
+                    const int32_t* __restrict__ cu_seq, const int32_t* __restrict__ ctx_lens,
+                    const int32_t* __restrict__ state_slots, float* S_state, float* n_state, float* m_state,
+                    float* __restrict__ o_raw, int H, int dk, int dv, float cap, float qscale) {
+  extern __shared__ __align__(16) float smem[];
+  const int dkp = dk + 4;
+  float* qs = smem;                                   // [16][dk + 4]   (16-byte aligned rows)
+  float* ks = qs + kChunkTok * dkp;                   // [16][dk + 4]
+  float* Ssm = ks + kChunkTok * dkp;                  // [dk][33]
+  float* vs = Ssm + dk * 33;                          // [16][32]
+  float* A = vs + kChunkTok * 32;                     // [16][16]
+  float* Wt = A + kChunkTok * 16;                     // [16][16]
+  float* Pp = Wt + kChunkTok * 16;                    // [4][16][32] partial S_0^T q_t
+  float* nsm = Pp + 4 * kChunkTok * 32;               // [dk]
+  float* ig = nsm + dk;                               // [16] each from here on
+  float* fg = ig + kChunkTok;
+  float* Fc = fg + kChunkTok;
+  float* mm = Fc + kChunkTok;
+  float* nq0 = mm + kChunkTok;
+  float* gl = nq0 + kChunkTok;
+  __shared__ float m_start;
+  const int s = blockIdx.x, h = blockIdx.y, z = blockIdx.z, Z = gridDim.z;
+  const int slot = state_slots[s];
+  if (slot < 0) return;
+  const int t0 = cu_seq[s], t1 = cu_seq[s + 1];
+  if (t1 <= t0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int c0 = z * 32;
+  float* Sp = S_state + ((size_t)slot * H + h) * dv * dk;
+  float* np = n_state + (((size_t)slot * H + h) * Z + z) * dk;
+  float* mp = m_state + ((size_t)slot * H + h) * Z + z;
+  const bool fresh = ctx_lens[s] == 0;
+  for (int i = tid; i < dk * 32; i += kChunkThreads) {
+    const int c = i / dk, r = i - c * dk;
+    Ssm[r * 33 + c] = (!fresh && c0 + c < dv) ? Sp[(size_t)(c0 + c) * dk + r] : 0.f;
+  }
+  for (int r = tid; r < dk; r += kChunkThreads) nsm[r] = fresh ? 0.f : np[r];
+  if (tid == 0) m_start = fresh ? 0.f : *mp;
+  const float bi = __bfloat162float(gate_bias[h]), bfg = __bfloat162float(gate_bias[H + h]);
+  // staging map: warp = token of the chunk, lane + 32 u = element of the head (no division)
+  TA rq[kChunkPre], rk[kChunkPre], rv;
+  float rgi = 0.f, rgf = 0.f;
+  auto fetch = [&](int ch, int nt) {
+    if (warp < nt) {
+      const TA* row = proj + (size_t)(ch + warp) * ld;
+#pragma unroll
+      for (int u = 0; u < kChunkPre; ++u) {
+        const int d = lane + 32 * u;
+        if (d < dk) {
+          rq[u] = row[q_col + h * dk + d];
+          rk[u] = row[k_col + h * dk + d];
+        }
+      }
+      if (c0 + lane < dv) rv = row[v_col + h * dv + c0 + lane];
+    }
+    if (tid < nt) {
+      const float* gr = gates + (size_t)(ch + tid) * 2 * H;
+      rgi = gr[h];
+      rgf = gr[H + h];
+    }
+  };
+  fetch(t0, min(kChunkTok, t1 - t0));
+  for (int ch = t0; ch < t1; ch += kChunkTok) {
+    const int nt = min(kChunkTok, t1 - ch);
+    __syncthreads();                                  // P4 of the previous chunk is done, inputs are free
+    // ---- P0
+    if (warp < nt) {
+#pragma unroll
+      for (int u = 0; u < kChunkPre; ++u) {
+        const int d = lane + 32 * u;
+        if (d < dk) {
+          qs[warp * dkp + d] = ml_f32(rq[u]) * qscale;
+          ks[warp * dkp + d] = ml_f32(rk[u]);
+        }
+      }
+    } else {
+      // rows of a short last chunk: zeros, so that the unconditional 16-token loops below add nothing
+#pragma unroll
+      for (int u = 0; u < kChunkPre; ++u) {
+        const int d = lane + 32 * u;
+        if (d < dk) qs[warp * dkp + d] = ks[warp * dkp + d] = 0.f;
+      }
+    }
+    vs[tid] = (warp < nt && c0 + lane < dv) ? ml_f32(rv) : 0.f;
+    if (tid < nt) {
+      ig[tid] = cap * tanhf((rgi + bi) / cap);
+      fg[tid] = log_sigmoid(cap * tanhf((rgf + bfg) / cap));
+    }
+    if (ch + kChunkTok < t1) fetch(ch + kChunkTok, min(kChunkTok, t1 - ch - kChunkTok));
+    __syncthreads();
+    // ---- P1
+    if (warp < 8) {
+      const int t = tid >> 4, sx = tid & 15;
+      float acc = 0.f;
+      if (t < nt && sx <= t) {
+        const float4* kr = reinterpret_cast<const float4*>(ks + sx * dkp);
+        const float4* qr = reinterpret_cast<const float4*>(qs + t * dkp);
+        for (int r4 = 0; r4 < dk / 4; ++r4) {
+          const float4 a = kr[r4], b = qr[r4];
+          acc = fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, fmaf(a.w, b.w, acc))));
+        }
+      }
+      A[t * 16 + sx] = acc;
+    } else if (warp < 12) {
+      const int tb = (warp - 8) * 4;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int r4 = lane; r4 < dk / 4; r4 += 32) {
+        const float4 nv = reinterpret_cast<const float4*>(nsm)[r4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float4 b = reinterpret_cast<const float4*>(qs + (tb + k) * dkp)[r4];
+          acc[k] = fmaf(nv.x, b.x, fmaf(nv.y, b.y, fmaf(nv.z, b.z, fmaf(nv.w, b.w, acc[k]))));
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float v = warp_sum(acc[k]);
+        if (lane == 0 && tb + k < nt) nq0[tb + k] = v;
+      }
+    } else if (tid == 12 * 32) {
+      float m = m_start, F = 0.f;
+      for (int t = 0; t < nt; ++t) {
+        m = fmaxf(fg[t] + m, ig[t]);
+        F += fg[t];
+        mm[t] = m;
+        Fc[t] = F;
+      }
+      const float mL = m, FL = F;
+      for (int t = 0; t < nt; ++t) gl[t] = expf(FL - Fc[t] + ig[t] - mL);
+    }
+    __syncthreads();
+    // ---- P2
+    if (tid < 256) {
+      const int t = tid >> 4, sx = tid & 15;
+      Wt[tid] = (t < nt && sx <= t) ? expf(Fc[t] - Fc[sx] + ig[sx] - mm[t]) * A[tid] : 0.f;
+    }
+    {
+      const int tg = warp & 3, rp = warp >> 2;          // tokens 4 tg .. 4 tg + 3, row groups rp, rp + 4, ...
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int r4 = rp; r4 < dk / 4; r4 += 4) {
+        const int r0 = r4 * 4;
+        const float s0 = Ssm[r0 * 33 + lane], s1 = Ssm[(r0 + 1) * 33 + lane], s2 = Ssm[(r0 + 2) * 33 + lane],
+                    s3 = Ssm[(r0 + 3) * 33 + lane];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float4 b = reinterpret_cast<const float4*>(qs + (tg * 4 + k) * dkp)[r4];
+          acc[k] = fmaf(s0, b.x, fmaf(s1, b.y, fmaf(s2, b.z, fmaf(s3, b.w, acc[k]))));
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) Pp[(rp * kChunkTok + tg * 4 + k) * 32 + lane] = acc[k];
+    }
+    __syncthreads();
+    // ---- P3
+    if (warp < nt) {
+      const int t = warp;
+      const float mt = mm[t];
+      const float d0 = expf(Fc[t] + m_start - mt);
+      float num = d0 * (Pp[t * 32 + lane] + Pp[(kChunkTok + t) * 32 + lane] + Pp[(2 * kChunkTok + t) * 32 + lane] +
+                        Pp[(3 * kChunkTok + t) * 32 + lane]);
+      float nqv = d0 * nq0[t];
+      for (int sx = 0; sx <= t; ++sx) {
+        const float wa = Wt[t * 16 + sx];
+        num = fmaf(wa, vs[sx * 32 + lane], num);
+        nqv += wa;
+      }
+      const float den = fmaxf(fabsf(nqv), expf(-mt)) + 1e-6f;
+      if (c0 + lane < dv) o_raw[(size_t)(ch + t) * H * dv + h * dv + c0 + lane] = num / den;
+    }
+    // ---- P4 (reads nothing that P3 writes; Ssm and nsm were last read before the barrier above)
+    {
+      const float dL = expf(Fc[nt - 1] + m_start - mm[nt - 1]);
+      float gv[kChunkTok];
+#pragma unroll
+      for (int sx = 0; sx < kChunkTok; ++sx) gv[sx] = sx < nt ? gl[sx] * vs[sx * 32 + lane] : 0.f;
+      for (int r4 = warp; r4 < dk / 4; r4 += kChunkThreads / 32) {
+        const int r0 = r4 * 4;
+        float a0 = dL * Ssm[r0 * 33 + lane], a1 = dL * Ssm[(r0 + 1) * 33 + lane], a2 = dL * Ssm[(r0 + 2) * 33 + lane],
+              a3 = dL * Ssm[(r0 + 3) * 33 + lane];
+#pragma unroll
+        for (int sx = 0; sx < kChunkTok; ++sx) {
+          const float4 kq = reinterpret_cast<const float4*>(ks + sx * dkp)[r4];   // rows beyond nt carry gv = 0
+          a0 = fmaf(kq.x, gv[sx], a0);
+          a1 = fmaf(kq.y, gv[sx], a1);
+          a2 = fmaf(kq.z, gv[sx], a2);
+          a3 = fmaf(kq.w, gv[sx], a3);
+        }
+        Ssm[r0 * 33 + lane] = a0;
+        Ssm[(r0 + 1) * 33 + lane] = a1;
+        Ssm[(r0 + 2) * 33 + lane] = a2;
+        Ssm[(r0 + 3) * 33 + lane] = a3;
+      }
+      for (int r = tid; r < dk; r += kChunkThreads) {
+        float acc = dL * nsm[r];
+        for (int sx = 0; sx < nt; ++sx) acc = fmaf(gl[sx], ks[sx * dkp + r], acc);
+        nsm[r] = acc;
+      }
+    }
+    __syncthreads();
+    if (tid == 0) m_start = mm[nt - 1];
+  }
+  __syncthreads();
+  for (int i = tid; i < dk * 32; i += kChunkThreads) {
+    const int c = i / dk, r = i - c * dk;
+    if (c0 + c < dv) Sp[(size_t)(c0 + c) * dk + r] = Ssm[r * 33 + c];
+  }
+  for (int r = tid; r < dk; r += kChunkThreads) np[r] = nsm[r];
+  if (tid == 0) *mp = m_start;
+}
+
 template <typename TA>
 static int launch_chunk(const void* proj, int64_t ld, int q_col, int k_col, int v_col, const float* gates,
                         const void* gate_bias, const int32_t* cu_seq, const int32_t* ctx_lens,
@@ -373,6 +594,16 @@ static int launch_chunk(const void* proj, int64_t ld, int q_col, int k_col, int 
   if (smem > 200 * 1024 || dk > kChunkPre * kChunkThreads / kChunkTok) {
     b200_set_error("mlstm_scan: key width %d exceeds %d", dk, kChunkPre * kChunkThreads / kChunkTok);
     return B200_ERR_UNSUPPORTED;
+  }
+  if (dk % 4 == 0) {
+    const size_t smem4 = sizeof(float) * ((size_t)2 * kChunkTok * (dk + 4) + (size_t)dk * 33 + kChunkTok * 32 +
+                                          2 * kChunkTok * 16 + 4 * kChunkTok * 32 + dk + 6 * kChunkTok);
+    if (smem4 > 48 * 1024)
+      cudaFuncSetAttribute(mlstm_chunk4_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4);
+    mlstm_chunk4_kernel<TA><<<grid, kChunkThreads, smem4, s>>>((const TA*)proj, ld, q_col, k_col, v_col, gates,
+                                                              (const bf16*)gate_bias, cu_seq, ctx_lens, state_slots,
+                                                              S_state, n_state, m_state, o_raw, H, dk, dv, cap, qscale);
+    return b200_check_launch("b200_mlstm_scan(chunk4)");
   }
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(mlstm_chunk_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
