@@ -159,12 +159,12 @@ def _kernel_numbers(size, T, B, ctx, log):
             + (f"{like_s * 1e6:9.1f} us {fl:6.3f}  -> {fl / fn:5.2f}x as far" if fl else "none"))
 
     # ---- norm after the sum vs add + RMSNorm
-    y, x32, w = rnd(T, D), rnd(T, D, dt=f32), rnd(D)
+    y, x32, w = rnd(T, D, dt=f32), rnd(T, D, dt=f32), rnd(D)      # the branch output enters the sum in fp32
     xb = torch.empty(T, D, device=dev, dtype=bf)
     t_new = _time(lambda: ops.sum_layer_norm(y, x32, w, 2.0, 1e-5, x_out=x32, xb_out=xb), flush)
     xr, rr = rnd(T, D), rnd(T, D)
     t_like = _time(lambda: ops.fused_add_rms_norm(xr, rr, w, 1e-5, out=xr, residual_out=rr), flush)
-    put("sum_layer_norm", t_new, T * D * 12.0, "fused_add_rms_norm", t_like, T * D * 8.0, "bytes")
+    put("sum_layer_norm", t_new, T * D * 14.0, "fused_add_rms_norm", t_like, T * D * 8.0, "bytes")
 
     # ---- projection post-processing + page scatter vs rotation + page scatter
     nblk = (B * ctx + T) // 16 + 8

@@ -14,8 +14,8 @@ decode steps and the sampler are shared -- with this family's layer sequence:
   mlstm mixer:     fp32 gate projection -> matrix-memory scan over every sequence's new rows (state slot in /
                    out, fp32) -> per-head unit RMS x norm weight x sigmoid gate.
 
-The residual stream is fp32 from the embedding to the final norm; projections read a copy rounded once to
-bf16.  With EngineConfig.dtype == "float32" every activation, cache and product is fp32 (CUDA-core GEMM with
+The residual stream is fp32 from the embedding to the final norm, and so is every sublayer's output on its way
+into the sum (the output projections write fp32); projections read a copy of the stream rounded once to bf16.  With EngineConfig.dtype == "float32" every activation, cache and product is fp32 (CUDA-core GEMM with
 FMA accumulation: no TF32, no bf16 anywhere but the stored weights, which convert exactly).
 """
 from __future__ import annotations
@@ -70,7 +70,7 @@ class LayerListRunner(ModelRunner):
         a = self.act_dtype
         self.resid32 = e(T, D, dt=torch.float32)          # the residual stream
         self.xb = e(T, D, dt=a)                           # the same rows as the projections read them
-        self.y = e(T, D, dt=a)                            # a sublayer's output
+        self.y = e(T, D, dt=torch.float32)                # a sublayer's output: fp32 into the residual sum
         self.proj = e(T * self.proj_width, dt=a)          # flat; viewed [T, rows of this layer's fused projection]
         self.mix_out = e(T * self.mix_width, dt=a)
         self.act = e(T * max(1, self.ff_width), dt=a)
