@@ -156,7 +156,9 @@ def main(argv: Optional[List[str]] = None) -> int:
         if args.model.startswith("random:"):
             mcfg, disk = (llama3_8b() if "8b" in args.model else tiny_llama()), None
         else:
-            mcfg = ModelConfig.from_pretrained(args.model)
+            mcfg = ModelConfig.from_pretrained(args.model)      # a Llama-class or a layer-list config, by config.json
+            if getattr(mcfg, "family", "") == "layer_list" and args.max_model_len is None:
+                args.max_model_len = 8192                       # the design has no position limit of its own
             disk = sum(f.stat().st_size for f in __import__("pathlib").Path(args.model).glob("*.safetensors")) or None
         ecfg = EngineConfig(model=args.model, tensor_parallel_size=args.tensor_parallel_size,
                             max_model_len=args.max_model_len, max_num_seqs=args.max_num_seqs,

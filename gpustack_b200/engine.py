@@ -184,7 +184,8 @@ class LLMEngine:
                  device: str = "cuda"):
         self.mcfg, self.ecfg, self.tp = mcfg, ecfg, tp
         if ecfg.max_model_len is None:
-            ecfg.max_model_len = mcfg.max_position_embeddings
+            # a layer-list design has no position limit of its own: 8192 unless the caller asks for more
+            ecfg.max_model_len = 8192 if getattr(mcfg, "family", "") == "layer_list" else mcfg.max_position_embeddings
         ecfg.max_model_len = min(ecfg.max_model_len, mcfg.max_position_embeddings)
         if mcfg.sliding_window and ecfg.max_model_len > mcfg.sliding_window:
             log.warning("sliding-window attention is not implemented: max_model_len capped at the window (%d)",

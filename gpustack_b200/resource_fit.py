@@ -47,8 +47,33 @@ class VramEstimate:
         return d
 
 
+def _layer_list_workspace(m, e: EngineConfig) -> int:
+    """Mirror of LayerListRunner._alloc_model_buffers / _alloc_step_io plus the recurrent state of every slot."""
+    T, S, D = max(e.max_num_batched_tokens, e.max_num_seqs), e.max_num_seqs, m.hidden_size
+    a = 4 if e.dtype == "float32" else 2
+    proj = mix = ff = gates = rec = 0
+    for l in m.layers:
+        x = l.mixer
+        if x.kind == "attention":
+            kv = 0 if x.kv_from is not None else x.kv_heads * (x.dim + x.vdim)
+            proj = max(proj, x.q_width + kv + (x.out_width if x.gate else 0))
+        else:
+            proj = max(proj, 2 * x.heads * x.dim + 2 * x.out_width)
+            gates, rec = max(gates, 2 * x.heads), max(rec, x.out_width)
+        mix = max(mix, x.out_width)
+        if l.mlp is not None:
+            ff = max(ff, l.mlp.ff)
+    S_smp = min(T, max(S, e.max_logit_rows or 0))
+    act = T * (D * (4 + a + 4) + (proj + mix + ff) * a + (gates + rec) * 4)
+    max_len = e.max_model_len or m.max_position_embeddings
+    staging = (3 * T + 10 * S + 3 * S_smp + S * math.ceil(max_len / e.block_size) + 2 * T) * 4
+    return act + S_smp * (D * a + m.vocab_size * 4) + staging + S * m.state_bytes_per_seq()
+
+
 def weight_bytes_per_gpu(m: ModelConfig, tp: int, quantization: Optional[str] = None) -> int:
     """Resident weight bytes of one rank (embedding and lm_head vocab-parallel, norms replicated)."""
+    if getattr(m, "family", "") == "layer_list":
+        return m.weight_bytes()
     H, I, L = m.hidden_size, m.intermediate_size, m.num_hidden_layers
     q = quantization or m.quantization
     lin_b = 1 if q == "fp8" else 2
@@ -68,6 +93,8 @@ def weight_bytes_per_gpu(m: ModelConfig, tp: int, quantization: Optional[str] = 
 
 def workspace_bytes_per_gpu(m: ModelConfig, e: EngineConfig, tp: int, quantization: Optional[str] = None) -> int:
     """Mirror of ModelRunner._alloc_workspace (runner.py)."""
+    if getattr(m, "family", "") == "layer_list":
+        return _layer_list_workspace(m, e)
     T = max(e.max_num_batched_tokens, e.max_num_seqs)
     S = e.max_num_seqs
     H, I = m.hidden_size, m.intermediate_size // tp
@@ -96,7 +123,8 @@ def estimate(m: ModelConfig, e: EngineConfig, weights_on_disk: Optional[int] = N
     tp = max(1, e.tensor_parallel_size)
     w = weight_bytes_per_gpu(m, tp, e.quantization)
     ws = workspace_bytes_per_gpu(m, e, tp, e.quantization)
-    kv_tok = m.kv_bytes_per_token(tp)
+    kv_tok = m.kv_bytes_per_token(tp, 4) if (getattr(m, "family", "") == "layer_list" and e.dtype == "float32") \
+        else m.kv_bytes_per_token(tp)
     max_len = min(e.max_model_len or m.max_position_embeddings, m.max_position_embeddings)
     kv_tokens = max_len if kv_tokens is None else max(int(kv_tokens), max_len)
     blocks = math.ceil(kv_tokens / e.block_size) + 1 + (e.max_num_seqs if kv_tokens > max_len else 0)

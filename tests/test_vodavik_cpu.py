@@ -173,3 +173,15 @@ def test_family_libraries_link_alone_and_export_what_the_runner_calls():
         for n in names:
             assert hasattr(h, n), (t, n)
     assert not hasattr(ctypes.CDLL(str(build.subset_lib(tag))), "b200_moe_route")
+
+
+def test_vram_estimate_covers_layer_list_models(tmp_path):
+    from gpustack_b200.config import EngineConfig
+    from gpustack_b200.resource_fit import estimate
+
+    c = LayerListConfig.from_dict(_cfg())
+    e16 = estimate(c, EngineConfig(max_model_len=256, max_num_seqs=4, max_num_batched_tokens=256))
+    e32 = estimate(c, EngineConfig(max_model_len=256, max_num_seqs=4, max_num_batched_tokens=256, dtype="float32"))
+    assert e16.weights == c.weight_bytes() and e16.kv_bytes_per_token == c.kv_bytes_per_token()
+    assert e32.kv_bytes_per_token == 2 * e16.kv_bytes_per_token and e32.workspace > e16.workspace
+    assert e16.workspace >= 4 * c.state_bytes_per_seq()
