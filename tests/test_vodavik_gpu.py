@@ -456,3 +456,23 @@ def test_float32_is_refused_by_families_without_a_32_bit_path():
     with pytest.raises(B200Error):
         LLMEngine.from_engine_config(EngineConfig(dtype="float32", max_num_seqs=2, num_gpu_blocks=16, max_model_len=64),
                                      mcfg=tiny_llama())
+
+
+def test_seeded_temperature_and_nucleus_sampling_through_the_engine():
+    """The family uses the engine's samplers unchanged: in-kernel Gumbel-max for plain temperature sampling (same
+    seed = same tokens whatever the batch), host re-sampling for nucleus requests; both differ from greedy."""
+    from gpustack_b200.scheduler import SamplingParams
+
+    cfg = cfg_tiles()
+    W = O.random_weights(cfg, seed=3)
+    prompts = [_tokens(cfg, n, 70 + n) for n in (9, 30, 18)]
+    eng = _engine(cfg, W, "bfloat16", seqs=4)
+    greedy = eng.generate(prompts, SamplingParams(max_tokens=16, ignore_eos=True))
+    hot = SamplingParams(max_tokens=16, ignore_eos=True, temperature=1.5, seed=123)
+    a = eng.generate(prompts, hot)
+    b = eng.generate(prompts[::-1], hot)[::-1]                       # other batch order, same seeds
+    assert a == b and a != greedy
+    nuc = SamplingParams(max_tokens=16, ignore_eos=True, temperature=1.5, top_p=0.8, seed=5)
+    c, d = eng.generate(prompts[:1], nuc), eng.generate(prompts[:1], nuc)
+    assert c == d and all(0 <= t < cfg["vocab"] for t in c[0])
+    assert eng.sched.slots.num_free == 4
