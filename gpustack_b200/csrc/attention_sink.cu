@@ -8,8 +8,8 @@
 //   * keys / values that belong to an earlier layer's cache (the caller passes that cache).
 // Three kernels: `attn_prep` (bias + norms + temperature, in place for q, scatter of k and v into
 // the pages), `prefill` (a tile of 16 query rows of one sequence per CTA, keys staged in shared
-// memory 32 at a time, online softmax) and `decode` (one query row per CTA, the four warps walk
-// interleaved keys and merge).  Scores, softmax statistics and the accumulator are fp32; the element
+// memory 32 at a time, online softmax) and `decode` (one query row per CTA, the four warps take
+// 32-key blocks in turn and merge).  Scores, softmax statistics and the accumulator are fp32; the element
 // type TA of the projection, the cache and the output is bf16, or fp32 for a model served in 32-bit.
 // Cache layout: K [blocks][G][page][dk], V [blocks][G][page][dv].
 #include "common.cuh"
@@ -303,50 +303,71 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
 
 // --------------------------------------------------------------------------------------- decode
 constexpr int kDecWarps = 4;
-constexpr int kMaxDkPerLane = 8;   // key width <= 256
 
-// grid (B, H): sequence b's single new row is row b of proj / out; it sees keys [0, seq_lens[b]).
-template <typename TA>
+// grid (B, H): sequence b's single new row is row b of proj / out; it sees keys [0, seq_lens[b]).  The four warps
+// take 32-key blocks in turn.  Scores: lane = key, the (scaled) query is broadcast from shared memory and every
+// lane walks its own key row (16-byte loads when VEC); one max / sum reduction per 32 keys.  Values: lane = column,
+// the 32 probabilities and page offsets go round by shuffle, value rows are read contiguously.
+template <typename TA, bool VEC>
 __global__ void __launch_bounds__(kDecWarps * 32)
 attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, const TA* __restrict__ k_cache,
                         const TA* __restrict__ v_cache, const int32_t* __restrict__ block_table, int max_blocks,
                         const int32_t* __restrict__ seq_lens, const float* __restrict__ sink, TA* out, int64_t ldo,
                         int H, int G, int dk, int dv, int page, float scale) {
   __shared__ float sm_m[kDecWarps], sm_l[kDecWarps];
-  extern __shared__ float sm_acc[];                   // [warps][dv]
+  extern __shared__ __align__(16) float sm_dyn[];      // [dk (padded to 8)] query, then [warps][dv] partial outputs
+  constexpr int E = 16 / (int)sizeof(TA);               // elements per 16-byte load
+  const int dkp = (dk + 7) & ~7;
+  float* qsm = sm_dyn;
+  float* sm_acc = sm_dyn + dkp;
   const int b = blockIdx.x, h = blockIdx.y, g = h / (H / G);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = seq_lens[b];
   const int32_t* bt = block_table + (size_t)b * max_blocks;
-  float q[kMaxDkPerLane];
-#pragma unroll
-  for (int c = 0; c < kMaxDkPerLane; ++c) {
-    const int d = lane + 32 * c;
-    q[c] = d < dk ? as_f32(proj[(size_t)b * ld + h * dk + d]) * scale : 0.f;
-  }
+  for (int d = threadIdx.x; d < dkp; d += blockDim.x)
+    qsm[d] = d < dk ? as_f32(proj[(size_t)b * ld + h * dk + d]) * scale : 0.f;
+  __syncthreads();
   float m = -CUDART_INF_F, l = 0.f, acc[kMaxDvPerLane];
   if (warp == 0 && sink != nullptr) { m = sink[h]; l = 1.f; }
 #pragma unroll
   for (int c = 0; c < kMaxDvPerLane; ++c) acc[c] = 0.f;
-  for (int key = warp; key < n; key += kDecWarps) {
-    const size_t base = ((size_t)bt[key / page] * G + g) * page + (key % page);
-    const TA* kp = k_cache + base * dk;
-    const TA* vp = v_cache + base * dv;
-    float sdot = 0.f;
+  for (int k0 = warp * 32; k0 < n; k0 += kDecWarps * 32) {
+    const int key = k0 + lane;
+    const bool live = key < n;
+    size_t base = 0;
+    float sc = -CUDART_INF_F;
+    if (live) {
+      base = ((size_t)bt[key / page] * G + g) * page + (key % page);
+      const TA* kp = k_cache + base * dk;
+      float a = 0.f;
+      if (VEC) {
+        for (int d = 0; d < dk; d += E) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(kp + d);
+          const TA* kv = reinterpret_cast<const TA*>(&raw);
 #pragma unroll
-    for (int c = 0; c < kMaxDkPerLane; ++c) {
-      const int d = lane + 32 * c;
-      if (d < dk) sdot = fmaf(q[c], as_f32(kp[d]), sdot);
+          for (int i = 0; i < E; ++i) a = fmaf(qsm[d + i], as_f32(kv[i]), a);
+        }
+      } else {
+        for (int d = 0; d < dk; ++d) a = fmaf(qsm[d], as_f32(kp[d]), a);
+      }
+      sc = a;
     }
-    sdot = warp_sum(sdot);
-    const float mn = fmaxf(m, sdot);
-    const float corr = expf(m - mn), p = expf(sdot - mn);
-    l = l * corr + p;
+    const float mn = fmaxf(m, warp_max(sc));            // finite: key k0 of this block is live
+    const float corr = expf(m - mn), p = live ? expf(sc - mn) : 0.f;
+    l = l * corr + warp_sum(p);
     m = mn;
 #pragma unroll
-    for (int c = 0; c < kMaxDvPerLane; ++c) {
-      const int d = lane + 32 * c;
-      if (d < dv) acc[c] = fmaf(p, as_f32(vp[d]), acc[c] * corr);
+    for (int c = 0; c < kMaxDvPerLane; ++c) acc[c] *= corr;
+    const int cnt = min(32, n - k0);
+    for (int j = 0; j < cnt; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+      const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);
+      const TA* vp = v_cache + (size_t)bj * dv;
+#pragma unroll
+      for (int c = 0; c < kMaxDvPerLane; ++c) {
+        const int d = lane + 32 * c;
+        if (d < dv) acc[c] = fmaf(pj, as_f32(vp[d]), acc[c]);
+      }
     }
   }
   if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
@@ -465,20 +486,21 @@ extern "C" int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int 
                                      const void* v_cache, const int32_t* block_table, int max_blocks,
                                      const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
                                      int G, int dk, int dv, int page, float scale, void* stream) {
-  B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dk <= 32 * kMaxDkPerLane && dv > 0 &&
-                   dv <= 32 * kMaxDvPerLane && page > 0,
+  B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 32 * kMaxDvPerLane && page > 0,
                "attn_sink_decode: bad shape H=%d G=%d dk=%d dv=%d", H, G, dk, dv);
   if (B <= 0) return B200_OK;
   cudaStream_t s = (cudaStream_t)stream;
-  const size_t smem = sizeof(float) * kDecWarps * dv;
+  const size_t smem = sizeof(float) * (((dk + 7) & ~7) + (size_t)kDecWarps * dv);
+  B200_REQUIRE(smem <= 48 * 1024, "attn_sink_decode: key width %d exceeds shared memory", dk);
+  const int esz = f32 ? 4 : 2;
+  const bool vec = (dk * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0;
   dim3 grid(B, H);
-  if (f32)
-    attn_sink_decode_kernel<float><<<grid, kDecWarps * 32, smem, s>>>(
-        (const float*)proj, ld, gate_col, (const float*)k_cache, (const float*)v_cache, block_table, max_blocks,
-        seq_lens, sink, (float*)out, ldo, H, G, dk, dv, page, scale);
-  else
-    attn_sink_decode_kernel<bf16><<<grid, kDecWarps * 32, smem, s>>>(
-        (const bf16*)proj, ld, gate_col, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, seq_lens,
-        sink, (bf16*)out, ldo, H, G, dk, dv, page, scale);
+#define B200_DEC(TA, V)                                                                                          \
+  attn_sink_decode_kernel<TA, V><<<grid, kDecWarps * 32, smem, s>>>(                                             \
+      (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, seq_lens,   \
+      sink, (TA*)out, ldo, H, G, dk, dv, page, scale)
+  if (f32) { if (vec) B200_DEC(float, true); else B200_DEC(float, false); }
+  else { if (vec) B200_DEC(bf16, true); else B200_DEC(bf16, false); }
+#undef B200_DEC
   return b200_check_launch("b200_attn_sink_decode");
 }
