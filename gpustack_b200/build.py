@@ -30,6 +30,10 @@ SOURCES = [
     "postnorm.cu",
     "attention_sink.cu",
     "mlstm.cu",
+    "streams.cu",
+    "latent.cu",
+    "gemm_simt_grouped.cu",
+    "moe_biased.cu",
 ]
 # What a layer-list decoder (attention with a softmax sink / matrix-memory recurrence, norm after the
 # sum) launches: a fresh checkout that only serves such a model compiles these and nothing else.
@@ -44,10 +48,25 @@ LAYER_LIST_SOURCES = [
 ]
 # ... plus the tensor-core attention kernels when some attention layer has tile-sized heads
 ATTENTION_TC_SOURCES = ["attention.cu", "attention_prefill_tc.cu"]
+# What a pre-norm decoder over residual streams with latent attention and gated / routed feed-forwards launches
+STREAMS_LATENT_SOURCES = [
+    "runtime.cu",
+    "elementwise.cu",
+    "gemm_tcgen05.cu",
+    "gemm_simt.cu",
+    "gemm_simt_grouped.cu",
+    "streams.cu",
+    "latent.cu",
+    "attention_sink.cu",
+]
+ROUTED_SOURCES = ["moe.cu", "moe_biased.cu"]
 
 
 def layer_list_sources(mcfg):
     """(tag, sources) of the library a process serving this layer-list model needs."""
+    if getattr(mcfg, "residual", "post_ln") == "streams":
+        routed = any(l.mlp is not None and l.mlp.kind == "moe" for l in mcfg.layers)
+        return ("streams_routed", STREAMS_LATENT_SOURCES + ROUTED_SOURCES) if routed else ("streams", list(STREAMS_LATENT_SOURCES))
     tc = any(l.mixer.kind == "attention" and l.mixer.tile_sized for l in mcfg.layers)
     return ("layer_list_tc", LAYER_LIST_SOURCES + ATTENTION_TC_SOURCES) if tc else ("layer_list", list(LAYER_LIST_SOURCES))
 

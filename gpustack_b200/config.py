@@ -15,7 +15,7 @@ from typing import Optional
 
 SUPPORTED_ARCHS = ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "MixtralForCausalLM")
 # designs whose config.json lists their layers one by one (LayerListConfig below)
-LAYER_LIST_ARCHS = ("Vodavik",)
+LAYER_LIST_ARCHS = ("Vodavik", "Danipel")
 
 
 @dataclass
@@ -262,9 +262,109 @@ class MLSTMSpec:
 
 
 @dataclass
-class MLPSpec:
-    kind: str                      # "dense": down(relu(up x)^2)
+class RotarySpec:
+    """Rotary position encoding of the first `dims` entries of a vector.  layout "interleaved" pairs entry 2i
+    with 2i+1, "half" pairs i with i + dims/2; frequencies base^(-2i/dims).  YaRN scaling (yarn_factor > 0):
+    with dim(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(dim(fast)), 0),
+    hi = min(ceil(dim(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at
+    f_i / factor * ramp_i + f_i (1 - ramp_i), and cos / sin are multiplied by 0.1 ln(factor) + 1."""
+    dims: int
+    base: float
+    layout: str = "interleaved"
+    yarn_factor: float = 0.0       # 0 = plain frequencies
+    yarn_original: float = 0.0
+    yarn_fast: float = 0.0
+    yarn_slow: float = 0.0
+
+    def frequencies(self):
+        """(fp64 list of dims/2 angular frequencies, the factor on cos and sin)."""
+        import math
+
+        half = self.dims // 2
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(half)]
+        if self.yarn_factor <= 0.0:
+            return f, 1.0
+
+        def turn_dim(t):
+            return self.dims * math.log(self.yarn_original / (2.0 * math.pi * t)) / (2.0 * math.log(self.base))
+
+        lo = max(math.floor(turn_dim(self.yarn_fast)), 0)
+        hi = min(math.ceil(turn_dim(self.yarn_slow)), self.dims - 1)
+        out = []
+        for i in range(half):
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f[i] / self.yarn_factor * ramp + f[i] * (1.0 - ramp))
+        return out, 0.1 * math.log(self.yarn_factor) + 1.0
+
+    def to_dict(self) -> dict:
+        d = {"base": self.base, "dims": self.dims}
+        if self.yarn_factor > 0.0:
+            d["scaling"] = {"factor": self.yarn_factor, "original": self.yarn_original, "fast": self.yarn_fast,
+                            "slow": self.yarn_slow}
+        return d
+
+
+@dataclass
+class LatentAttentionSpec:
+    """Attention whose keys and values are expanded from one latent per token: the cache holds, per token
+    and layer, the RMS-normed latent c (kv_rank wide) and ONE rotated key part (rot_dim wide) shared by
+    all heads.  Per head: key = [W_uk c | rotated part], value = W_uv c, query = [dim unrotated | rot_dim
+    rotated]; q_rank > 0: queries go through their own RMS-normed latent.  sink: a learned per-head
+    term exp(sink_h) in the softmax denominator."""
+    heads: int
+    dim: int                       # unrotated query / key width per head
+    rot_dim: int                   # rotated query / key width per head (one shared key part)
+    vdim: int
+    kv_rank: int
+    scale: float
+    rot: RotarySpec = None
+    q_rank: int = 0                # 0 = queries straight from the mixer input
+    sink: bool = False
+    type_name: str = "latent_attention"
+
+    kind = "latent_attention"
+
+    @property
+    def q_width(self) -> int:
+        return self.heads * (self.dim + self.rot_dim)
+
+    @property
+    def cache_width(self) -> int:
+        return self.kv_rank + self.rot_dim
+
+    @property
+    def out_width(self) -> int:
+        return self.heads * self.vdim
+
+    @property
+    def proj_rows(self) -> int:
+        """Rows of the fused projection that reads the mixer input: [q or the query latent | latent + key part]."""
+        return (self.q_rank if self.q_rank else self.q_width) + self.cache_width
+
+
+@dataclass
+class MoESpec:
+    """Routed feed-forward: softmax over experts + identity router outputs; the `top` largest of score +
+    correction are chosen, weighted by score / (sum of the chosen scores + 1e-20) * scale.  The last `identity`
+    router outputs return the input itself.  An expert is  down(g sigmoid(1.702 g) (u + 1))  with
+    g = min(gate x, limit), u = clamp(up x, -limit, limit); a shared expert of the same form (shared_ff > 0)
+    runs for every token."""
+    experts: int
+    top: int
     ff: int
+    limit: float
+    identity: int = 0
+    scale: float = 1.0
+    shared_ff: int = 0
+    shared_limit: float = 0.0
+
+
+@dataclass
+class MLPSpec:
+    kind: str                      # "dense" | "moe"
+    ff: int                        # dense: hidden width; moe: the widest hidden width (expert or shared)
+    act: str = "relu2"             # dense: "relu2" = down(relu(up x)^2); "gelu_tanh" = down(gelu(gate x) * up x)
+    moe: Optional[MoESpec] = None
 
 
 @dataclass
@@ -285,6 +385,14 @@ class LayerListConfig:
     norm_eps: float = 1e-5
     postln_alpha: float = 1.0
     logit_scale: float = 1.0
+    # residual scheme: "post_ln" (x <- LN(alpha x + f(x))) or "streams" (pre-norm; `streams` parallel copies of
+    # the residual joined by learned scalars: u = sum_s in[s] x_s, y = f(norm(u)),
+    # x_t <- sum_s mix[s, t] x_s + residual_mult * out[t] * y; streams == 0: one stream, x <- x + residual_mult * y)
+    residual: str = "post_ln"
+    norm: str = "layernorm"                    # "layernorm" (bias-free) | "tanh": tanh(alpha x) w + b, no statistics
+    streams: int = 0
+    residual_mult: float = 1.0
+    embed_scale: float = 1.0
     max_position_embeddings: int = 1 << 20     # the design has no learned or tabulated positions
     eos_token_id: Optional[int] = None
     bos_token_id: Optional[int] = None
@@ -313,9 +421,15 @@ class LayerListConfig:
             return None
         return l if m.kv_from is None else int(m.kv_from)
 
+    @property
+    def n_streams(self) -> int:
+        """Copies of the residual stream the runner keeps (1 unless the design has hyper-connections)."""
+        return max(1, self.streams)
+
     def kv_bytes_per_token(self, tp: int = 1, elem_bytes: int = 2) -> int:
-        return sum(m.kv_heads * (m.dim + m.vdim) * elem_bytes for m in (l.mixer for l in self.layers)
-                   if m.kind == "attention" and m.kv_from is None)
+        n = sum(m.kv_heads * (m.dim + m.vdim) * elem_bytes for m in (l.mixer for l in self.layers)
+                if m.kind == "attention" and m.kv_from is None)
+        return n + sum(m.cache_width * elem_bytes for m in (l.mixer for l in self.layers) if m.kind == "latent_attention")
 
     def state_bytes_per_seq(self) -> int:
         n = 0
@@ -332,10 +446,16 @@ class LayerListConfig:
             if m.kind == "attention":
                 kv = 0 if m.kv_from is not None else m.kv_heads * (m.dim + m.vdim)
                 n += D * (m.q_width + kv + (m.out_width if m.gate else 0)) + m.out_width * D
+            elif m.kind == "latent_attention":
+                n += D * m.proj_rows + (m.q_rank * m.q_width if m.q_rank else 0) \
+                    + m.kv_rank * m.heads * (m.dim + m.vdim) + m.out_width * D
             else:
                 n += D * (2 * m.heads * m.dim + 2 * m.out_width + 2 * m.heads) + m.out_width * D
-            if l.mlp is not None:
-                n += 2 * D * l.mlp.ff
+            if l.mlp is not None and l.mlp.kind == "moe":
+                e = l.mlp.moe
+                n += 3 * D * (e.experts * e.ff + e.shared_ff) + (e.experts + e.identity) * D
+            elif l.mlp is not None:
+                n += (2 if l.mlp.act == "relu2" else 3) * D * l.mlp.ff
         return 2 * (n + self.vocab_size * D)
 
     @staticmethod
@@ -343,6 +463,8 @@ class LayerListConfig:
         arch = architecture_of(d)
         if arch not in LAYER_LIST_ARCHS:
             raise ValueError(f"unsupported architecture {arch}; layer-list designs: {LAYER_LIST_ARCHS}")
+        if arch == "Danipel":
+            return _danipel_from_dict(d)
         layers = []
         for i, e in enumerate(d["layers"]):
             mx = e["mixer"]
@@ -379,6 +501,8 @@ class LayerListConfig:
 
     def to_dict(self) -> dict:
         """config.json of this model (the inverse of from_dict)."""
+        if self.architecture == "Danipel":
+            return _danipel_to_dict(self)
         out = []
         for l in self.layers:
             m = l.mixer
@@ -394,6 +518,80 @@ class LayerListConfig:
                         "mlp": None if l.mlp is None else {"kind": l.mlp.kind, "ff": l.mlp.ff}})
         return {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size, "layers": out,
                 "norm": {"eps": self.norm_eps}, "postln_alpha": self.postln_alpha, "logit_scale": self.logit_scale}
+
+
+def _eos_of(d: dict):
+    eos = d.get("eos_token_id")
+    return tuple(int(t) for t in eos) if isinstance(eos, list) else (() if eos is None else (int(eos),))
+
+
+def _danipel_from_dict(d: dict) -> "LayerListConfig":
+    """Danipel: pre-norm layers over `streams` residual copies, tanh norm, latent attention mixers
+    ("latent_attention": direct queries, interleaved rotation, optional YaRN, softmax sink;
+    "latent_attention_2": latent queries, half-split rotation, plain softmax), dense gated-GELU or routed
+    feed-forward."""
+    layers = []
+    for i, e in enumerate(d["layers"]):
+        mx, kind = e["mixer"], e["type"]
+        if kind not in ("latent_attention", "latent_attention_2"):
+            raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+        two = kind == "latent_attention_2"
+        r = mx["rot"]
+        sc = r.get("scaling") or {}
+        rot = RotarySpec(dims=int(r["dims"]), base=float(r["base"]), layout="half" if two else "interleaved",
+                         yarn_factor=float(sc.get("factor", 0.0)), yarn_original=float(sc.get("original", 0.0)),
+                         yarn_fast=float(sc.get("fast", 0.0)), yarn_slow=float(sc.get("slow", 0.0)))
+        spec = LatentAttentionSpec(heads=int(mx["heads"]), dim=int(mx["dim"]), rot_dim=int(mx["rot_dim"]),
+                                   vdim=int(mx["vdim"]), kv_rank=int(mx["kv_rank"]), scale=float(mx["scale"]), rot=rot,
+                                   q_rank=int(mx["q_rank"]) if two else 0, sink=not two, type_name=kind)
+        if rot.dims % 2 or rot.dims > spec.rot_dim or rot.dims <= 0:
+            raise ValueError(f"layer {i}: rot.dims {rot.dims} must be even and at most rot_dim {spec.rot_dim}")
+        mlp = e.get("mlp")
+        if mlp is not None:
+            if mlp.get("kind") == "dense":
+                mlp = MLPSpec(kind="dense", ff=int(mlp["ff"]), act="gelu_tanh")
+            elif mlp.get("kind") == "moe":
+                ro, ex, sh = mlp["router"], mlp["expert"], mlp.get("shared") or None
+                moe = MoESpec(experts=int(ro["experts"]), top=int(ro["top"]), ff=int(ex["ff"]), limit=float(ex["limit"]),
+                              identity=int(ro.get("identity") or 0), scale=float(ro.get("scale", 1.0)),
+                              shared_ff=int(sh["ff"]) if sh else 0, shared_limit=float(sh["limit"]) if sh else 0.0)
+                if not 1 <= moe.top <= moe.experts + moe.identity:
+                    raise ValueError(f"layer {i}: top {moe.top} of {moe.experts + moe.identity} router outputs")
+                mlp = MLPSpec(kind="moe", ff=max(moe.ff, moe.shared_ff), act="clamped_swish", moe=moe)
+            else:
+                raise ValueError(f"layer {i}: unknown feed-forward kind {mlp.get('kind')!r}")
+        layers.append(LayerSpec(mixer=spec, mlp=mlp))
+    eos_all = _eos_of(d)
+    return LayerListConfig(architecture="Danipel", vocab_size=int(d["vocab"]), hidden_size=int(d["width"]), layers=layers,
+                           norm_eps=float(d["norm"]["eps"]), residual="streams", norm="tanh",
+                           streams=int(d.get("streams") or 0), residual_mult=float(d.get("residual_mult", 1.0)),
+                           embed_scale=float((d.get("embedding") or {}).get("scale", 1.0)), eos_token_ids=eos_all,
+                           eos_token_id=eos_all[0] if eos_all else None, bos_token_id=d.get("bos_token_id"))
+
+
+def _danipel_to_dict(c: "LayerListConfig") -> dict:
+    out = []
+    for l in c.layers:
+        m = l.mixer
+        mx = {"heads": m.heads, "dim": m.dim, "rot_dim": m.rot_dim, "vdim": m.vdim, "kv_rank": m.kv_rank,
+              "scale": m.scale, "rot": m.rot.to_dict()}
+        if m.q_rank:
+            mx["q_rank"] = m.q_rank
+        mlp = None
+        if l.mlp is not None and l.mlp.kind == "dense":
+            mlp = {"kind": "dense", "ff": l.mlp.ff}
+        elif l.mlp is not None:
+            e = l.mlp.moe
+            mlp = {"kind": "moe", "expert": {"ff": e.ff, "limit": e.limit},
+                   "router": {"experts": e.experts, "identity": e.identity, "scale": e.scale, "top": e.top}}
+            if e.shared_ff:
+                mlp["shared"] = {"ff": e.shared_ff, "limit": e.shared_limit}
+        out.append({"type": m.type_name, "mixer": mx, "mlp": mlp})
+    d = {"architecture": "Danipel", "vocab": c.vocab_size, "width": c.hidden_size, "layers": out,
+         "norm": {"eps": c.norm_eps}, "residual_mult": c.residual_mult, "embedding": {"scale": c.embed_scale}}
+    if c.streams:
+        d["streams"] = c.streams
+    return d
 
 
 # Named shapes used by tests and bench (random-init; there are no checkpoints offline).

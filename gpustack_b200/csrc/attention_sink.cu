@@ -11,7 +11,9 @@
 // memory 32 at a time, online softmax) and `decode` (one query row per CTA, the four warps take
 // 32-key blocks in turn and merge).  Scores, softmax statistics and the accumulator are fp32; the element
 // type TA of the projection, the cache and the output is bf16, or fp32 for a model served in 32-bit.
-// Cache layout: K [blocks][G][page][dk], V [blocks][G][page][dv].
+// Cache layout: K [blocks][G][page][dk], V [blocks][G][page][dv]; v_ld (value row pitch) lets the values be a
+// slice of another array with wider rows -- the first dv entries of the key rows when v_cache == k_cache and
+// v_ld == dk, which is how a latent cache (one shared row per token, G = 1) is read.
 #include "common.cuh"
 #include "runtime.h"
 #include "../../include/b200.h"
@@ -188,7 +190,7 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
                          const int32_t* __restrict__ cu_q, const int32_t* __restrict__ ctx_lens,
                          const int32_t* __restrict__ tile_seq, const int32_t* __restrict__ tile_q0,
                          const float* __restrict__ sink, TA* out, int64_t ldo, int H, int G, int dk, int dv, int page,
-                         float scale) {
+                         float scale, int64_t v_ld) {
   extern __shared__ float smem[];
   float* Qs = smem;                                   // [16][dk]
   float* Ks = Qs + kPfRows * dk;                      // [32][dk + 1]
@@ -225,7 +227,7 @@ attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, 
       if (key < kv_end) {
         const size_t base = ((size_t)bt[key / page] * G + g) * page + (key % page);
         const TA* kp = k_cache + base * dk;
-        const TA* vp = v_cache + base * dv;
+        const TA* vp = v_cache + base * v_ld;
         for (int d = lane; d < dk; d += 32) Ks[j * (dk + 1) + d] = as_f32(kp[d]);
         for (int d = lane; d < dv; d += 32) Vs[j * dv + d] = as_f32(vp[d]);
       } else {
@@ -313,7 +315,7 @@ __global__ void __launch_bounds__(kDecWarps * 32)
 attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, const TA* __restrict__ k_cache,
                         const TA* __restrict__ v_cache, const int32_t* __restrict__ block_table, int max_blocks,
                         const int32_t* __restrict__ seq_lens, const float* __restrict__ sink, TA* out, int64_t ldo,
-                        int H, int G, int dk, int dv, int page, float scale) {
+                        int H, int G, int dk, int dv, int page, float scale, int64_t v_ld) {
   __shared__ float sm_m[kDecWarps], sm_l[kDecWarps];
   extern __shared__ __align__(16) float sm_dyn[];      // [dk (padded to 8)] query, then [warps][dv] partial outputs
   constexpr int E = 16 / (int)sizeof(TA);               // elements per 16-byte load
@@ -362,7 +364,7 @@ attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, c
     for (int j = 0; j < cnt; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);
-      const TA* vp = v_cache + (size_t)bj * dv;
+      const TA* vp = v_cache + (size_t)bj * v_ld;
 #pragma unroll
       for (int c = 0; c < kMaxDvPerLane; ++c) {
         const int d = lane + 32 * c;
@@ -455,7 +457,10 @@ extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int
                                       const void* v_cache, const int32_t* block_table, int max_blocks,
                                       const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
                                       const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
-                                      int64_t ldo, int H, int G, int dk, int dv, int page, float scale, void* stream) {
+                                      int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
+                                      void* stream) {
+  if (v_ld <= 0) v_ld = dv;
+  B200_REQUIRE(v_ld >= dv, "attn_sink_prefill: value row pitch %lld < dv=%d", (long long)v_ld, dv);
   B200_REQUIRE(tile_rows > 0 && tile_rows % kPfRows == 0, "attn_sink_prefill: tiles of %d rows (multiples of %d)",
                tile_rows, kPfRows);
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 32 * kMaxDvPerLane && page > 0,
@@ -471,13 +476,13 @@ extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int
       cudaFuncSetAttribute(attn_sink_prefill_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attn_sink_prefill_kernel<float><<<grid, kPfWarps * 32, smem, s>>>(
         (const float*)proj, ld, gate_col, (const float*)k_cache, (const float*)v_cache, block_table, max_blocks, cu_q,
-        ctx_lens, tile_seq, tile_q0, sink, (float*)out, ldo, H, G, dk, dv, page, scale);
+        ctx_lens, tile_seq, tile_q0, sink, (float*)out, ldo, H, G, dk, dv, page, scale, v_ld);
   } else {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(attn_sink_prefill_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attn_sink_prefill_kernel<bf16><<<grid, kPfWarps * 32, smem, s>>>(
         (const bf16*)proj, ld, gate_col, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, cu_q,
-        ctx_lens, tile_seq, tile_q0, sink, (bf16*)out, ldo, H, G, dk, dv, page, scale);
+        ctx_lens, tile_seq, tile_q0, sink, (bf16*)out, ldo, H, G, dk, dv, page, scale, v_ld);
   }
   return b200_check_launch("b200_attn_sink_prefill");
 }
@@ -485,7 +490,9 @@ extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int
 extern "C" int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
                                      const void* v_cache, const int32_t* block_table, int max_blocks,
                                      const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
-                                     int G, int dk, int dv, int page, float scale, void* stream) {
+                                     int G, int dk, int dv, int page, float scale, int64_t v_ld, void* stream) {
+  if (v_ld <= 0) v_ld = dv;
+  B200_REQUIRE(v_ld >= dv, "attn_sink_decode: value row pitch %lld < dv=%d", (long long)v_ld, dv);
   B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 32 * kMaxDvPerLane && page > 0,
                "attn_sink_decode: bad shape H=%d G=%d dk=%d dv=%d", H, G, dk, dv);
   if (B <= 0) return B200_OK;
@@ -498,7 +505,7 @@ extern "C" int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int 
 #define B200_DEC(TA, V)                                                                                          \
   attn_sink_decode_kernel<TA, V><<<grid, kDecWarps * 32, smem, s>>>(                                             \
       (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, seq_lens,   \
-      sink, (TA*)out, ldo, H, G, dk, dv, page, scale)
+      sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld)
   if (f32) { if (vec) B200_DEC(float, true); else B200_DEC(float, false); }
   else { if (vec) B200_DEC(bf16, true); else B200_DEC(bf16, false); }
 #undef B200_DEC

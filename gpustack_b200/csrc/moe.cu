@@ -15,7 +15,7 @@
 
 namespace b200 {
 
-constexpr int kMaxExperts = 64;
+constexpr int kMaxExperts = 256;
 constexpr int kMaxTopK = 8;
 
 // ---------------------------------------------------------------------------------------------

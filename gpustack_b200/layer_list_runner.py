@@ -1,4 +1,4 @@
-"""Model runner of the layer-list decoders (config.LayerListConfig: Vodavik).
+"""Model runner of the layer-list decoders (config.LayerListConfig: Vodavik, Danipel).
 
 Same step interface as runner.ModelRunner -- the engine, the scheduler's plans, the staging buffer, CUDA-graph
 decode steps and the sampler are shared -- with this family's layer sequence:
@@ -13,6 +13,21 @@ decode steps and the sampler are shared -- with this family's layer sequence:
                    a `kv_from` layer skips the scatter and reads the owner layer's pages.
   mlstm mixer:     fp32 gate projection -> matrix-memory scan over every sequence's new rows (state slot in /
                    out, fp32) -> per-head unit RMS x norm weight x sigmoid gate.
+
+  latent_attention mixer: fused projection [q or query latent | latent | key part] (-> RMS norm -> query
+                   up-projection) -> latent_prep (latent norm + rotated key part into the token's ONE cache row,
+                   rotated query parts) -> per-head absorption of W_uk into the query -> attention over the latent
+                   cache (one shared row per token: G = 1, values = the first kv_rank entries of the key rows;
+                   softmax sink optional) -> per-head W_uv -> output projection.
+
+Residual schemes (config.residual): "post_ln" as drawn above; "streams": pre-norm over S fp32 residual copies,
+
+    embed * scale -> S streams -> per sublayer [ u = sum_s in[s] x_s -> tanh norm -> sublayer ->
+                                                 x_t <- sum_s mix[s,t] x_s + m out[t] y ]  -> sum of the streams -> tanh norm
+
+where ONE streams_step launch does a sublayer's write-back and the next sublayer's read + norm.  Feed-forwards:
+relu^2 (ungated), gated GELU, or a routed mixture of clamped gated experts with identity experts and a shared
+expert (ops.routed_experts).
 
 The residual stream is fp32 from the embedding to the final norm, and so is every sublayer's output on its way
 into the sum (the output projections write fp32); projections read a copy of the stream rounded once to bf16.  With EngineConfig.dtype == "float32" every activation, cache and product is fp32 (CUDA-core GEMM with
@@ -55,9 +70,18 @@ class LayerListRunner(ModelRunner):
         if self.prefill_tile % base:
             raise B200Error("prefill tile sizes of the attention kernels do not nest")
         self._dec_ws = {}
+        self.streams = cfg.residual == "streams"
+        self.S = cfg.n_streams if self.streams else 1
         self.proj_width = max(lw.proj.shape[0] for lw in self.w.layers)
         self.mix_width = max(l.mixer.out_width for l in cfg.layers)
-        self.ff_width = max([l.mlp.ff for l in cfg.layers if l.mlp is not None] or [0])
+        self.ff_width = max([(l.mlp.moe.shared_ff if l.mlp.kind == "moe" else l.mlp.ff) for l in cfg.layers
+                             if l.mlp is not None] or [0])
+        lat = [l.mixer for l in cfg.layers if l.mixer.kind == "latent_attention"]
+        self.lat_q_width = max([m.q_width for m in lat if m.q_rank] or [0])
+        self.lat_q_rank = max([m.q_rank for m in lat] or [0])
+        self.lat_qa_width = max([m.heads * m.cache_width for m in lat] or [0])
+        self.lat_o_width = max([m.heads * m.kv_rank for m in lat] or [0])
+        self.routed = [l.mlp.moe for l in cfg.layers if l.mlp is not None and l.mlp.kind == "moe"]
         rec = [l.mixer for l in cfg.layers if l.mixer.kind == "mlstm"]
         self.gate_width = max([2 * m.heads for m in rec] or [0])
         self.rec_width = max([m.out_width for m in rec] or [0])
@@ -68,7 +92,7 @@ class LayerListRunner(ModelRunner):
         dev, T, D = self.device, self.max_tokens, self.H
         e = lambda *s, dt: torch.empty(*s, dtype=dt, device=dev)   # noqa: E731
         a = self.act_dtype
-        self.resid32 = e(T, D, dt=torch.float32)          # the residual stream
+        self.resid32 = e(T, self.S * D, dt=torch.float32)  # the residual stream (S copies per row with hyper-connections)
         self.xb = e(T, D, dt=a)                           # the same rows as the projections read them
         self.y = e(T, D, dt=torch.float32)                # a sublayer's output: fp32 into the residual sum
         self.proj = e(T * self.proj_width, dt=a)          # flat; viewed [T, rows of this layer's fused projection]
@@ -76,6 +100,15 @@ class LayerListRunner(ModelRunner):
         self.act = e(T * max(1, self.ff_width), dt=a)
         self.gates = e(T * max(1, self.gate_width), dt=torch.float32)
         self.o_raw = e(T * max(1, self.rec_width), dt=torch.float32)
+        self.lat_q = e(T * max(1, self.lat_q_width), dt=a)        # queries of a mixer whose queries have a latent
+        self.lat_cq = e(T * max(1, self.lat_q_rank), dt=a)        # the normed query latent
+        self.lat_qa = e(T * max(1, self.lat_qa_width), dt=a)      # absorbed queries [H][kv_rank | rot_dim]
+        self.lat_o = e(T * max(1, self.lat_o_width), dt=a)        # attention output in latent space [H][kv_rank]
+        self.routed_ws = None
+        if self.routed:
+            self.routed_ws = ops.RoutedWorkspace(T, max(r.top for r in self.routed),
+                                                 max(r.experts + r.identity for r in self.routed), D,
+                                                 max(r.ff for r in self.routed), a, dev)
 
     def _alloc_step_io(self):
         super()._alloc_step_io()
@@ -97,6 +130,11 @@ class LayerListRunner(ModelRunner):
                                               device=self.device)
                 self.v_cache[l] = torch.zeros(num_blocks, m.kv_heads, self.block_size, m.vdim, dtype=self.act_dtype,
                                               device=self.device)
+            elif m.kind == "latent_attention":
+                # ONE row per token for all heads: [latent: kv_rank | rotated key part: rot_dim]; the values are its head
+                self.k_cache[l] = torch.zeros(num_blocks, 1, self.block_size, m.cache_width, dtype=self.act_dtype,
+                                              device=self.device)
+                self.v_cache[l] = self.k_cache[l]
         for l, layer in enumerate(cfg.layers):
             m = layer.mixer
             if m.kind == "attention" and m.kv_from is not None:
@@ -123,7 +161,33 @@ class LayerListRunner(ModelRunner):
         return buf[:T * n].view(T, n)
 
     def _embed(self, ids: torch.Tensor, T: int) -> None:
+        if self.streams:
+            lw = self.w.layers[0]
+            ops.embed_streams(ids, self.w.embed, self.resid32[:T], self.S, self.mcfg.embed_scale)
+            ops.streams_step(self.resid32[:T], self.S, hc_read=lw.hc1, norm=(lw.norm1_alpha, lw.norm1, lw.norm1_b),
+                             xb_out=self.xb[:T])
+            self.stats["kernel_launches"] += 2
+            return
         ops.embed_rows(ids, self.w.embed, self.resid32[:T], self.xb[:T])
+        self.stats["kernel_launches"] += 1
+
+    def _join(self, T: int, l: int, q: int) -> None:
+        """The branch output self.y of sublayer q (1 mixer, 2 feed-forward) of layer l enters the residual, and the
+        next sublayer's input is prepared in self.xb."""
+        cfg, lw = self.mcfg, self.w.layers[l]
+        if not self.streams:
+            self._post(T, lw.norm1 if q == 1 else lw.norm2)
+            self.stats["kernel_launches"] += 1
+            return
+        if q == 1 and cfg.layers[l].mlp is not None:
+            nxt = (lw.hc2, (lw.norm2_alpha, lw.norm2, lw.norm2_b))
+        elif l + 1 < len(cfg.layers):
+            n = self.w.layers[l + 1]
+            nxt = (n.hc1, (n.norm1_alpha, n.norm1, n.norm1_b))
+        else:
+            nxt = (None, None)          # the last sublayer: the final norm runs on the wanted rows only
+        ops.streams_step(self.resid32[:T], self.S, y=self.y[:T], hc_write=lw.hc1 if q == 1 else lw.hc2,
+                         mult=cfg.residual_mult, hc_read=nxt[0], norm=nxt[1], xb_out=self.xb[:T] if nxt[1] else None)
         self.stats["kernel_launches"] += 1
 
     def _post(self, T: int, norm_w: torch.Tensor) -> None:
@@ -156,7 +220,9 @@ class LayerListRunner(ModelRunner):
             proj = self._view(self.proj, T, lw.proj.shape[0])
             out = self._view(self.mix_out, T, m.out_width)
             ops.linear(self.xb[:T], lw.proj, proj)
-            if m.kind == "attention":
+            if m.kind == "latent_attention":
+                self._latent_attention(l, m, lw, proj, out, T, Tp, Bd, nt, bt_p, cu_p, ctx_p, ts, tq, lens_d, bt_d)
+            elif m.kind == "attention":
                 own = m.kv_from is None
                 H, G, dk, dv = m.heads, m.kv_heads, m.dim, m.vdim
                 ops.attn_prep(proj, lw.proj_bias, lw.q_norm, lw.k_norm, pos, slots, self.k_cache[l] if own else None,
@@ -189,14 +255,64 @@ class LayerListRunner(ModelRunner):
                 ops.mlstm_out(o_raw, proj, 2 * H * dk + H * dv, lw.out_norm, out, H, dv, eps)
                 self.stats["kernel_launches"] += 4
             ops.linear(out, lw.o, self.y[:T])
-            self._post(T, lw.norm1)
-            self.stats["kernel_launches"] += 2
+            self.stats["kernel_launches"] += 1
+            self._join(T, l, 1)
             if layer.mlp is not None:
-                act = self._view(self.act, T, layer.mlp.ff)
-                ops.linear(self.xb[:T], lw.up, act, relu2=True)        # squared ReLU in the GEMM's epilogue
-                ops.linear(act, lw.down, self.y[:T])
-                self._post(T, lw.norm2)
-                self.stats["kernel_launches"] += 3
+                self._feed_forward(T, layer.mlp, lw)
+                self._join(T, l, 2)
+
+    def _latent_attention(self, l, m, lw, proj, out, T, Tp, Bd, nt, bt_p, cu_p, ctx_p, ts, tq, lens_d, bt_d) -> None:
+        """Latent attention in the absorbed form: scores and values are taken straight from the cached latent rows,
+        W_uk is folded into the query before and W_uv applied to the latent-space output after the attention, so a
+        head's keys and values are never expanded and every head reads the same cache row."""
+        eps = self.mcfg.norm_eps
+        H, dn, dr, R, dv = m.heads, m.dim, m.rot_dim, m.kv_rank, m.vdim
+        W = R + dr
+        if m.q_rank:
+            cq = self._view(self.lat_cq, T, m.q_rank)
+            ops.rms_rows(proj[:, :m.q_rank], lw.q_lat_norm, cq, eps)
+            q = self._view(self.lat_q, T, m.q_width)
+            ops.linear(cq, lw.uq, q)
+            kv_col = m.q_rank
+            self.stats["kernel_launches"] += 2
+        else:
+            q, kv_col = proj[:, :m.q_width], m.q_width
+        qa = self._view(self.lat_qa, T, H * W)
+        o_lat = self._view(self.lat_o, T, H * R)
+        cache = self.k_cache[l]
+        ops.latent_prep(proj, kv_col, q, lw.kv_norm, self._pos, self._slots, cache, qa, H, dn, dr, R, m.rot.dims,
+                        m.rot.layout == "half", lw.rot_freq, lw.rot_mag, eps)
+        ops.head_linear(q, lw.uk_t, qa, H, n=R, k=dn, x_head=dn + dr, out_head=W)
+        if nt:
+            ops.attn_sink_prefill(qa[:Tp], -1, cache, cache, bt_p, cu_p, ctx_p, ts, tq, lw.sink, o_lat[:Tp], H, 1, W, R,
+                                  m.scale, tile_rows=self.prefill_tile, v_ld=W)
+        if Bd:
+            ops.attn_sink_decode(qa[Tp:T], -1, cache, cache, bt_d, lens_d, lw.sink, o_lat[Tp:T], H, 1, W, R, m.scale, v_ld=W)
+        ops.head_linear(o_lat, lw.uv, out, H, n=dv, k=R, x_head=R, out_head=dv)
+        self.stats["kernel_launches"] += 3 + (1 if nt else 0) + (1 if Bd else 0)
+
+    def _feed_forward(self, T: int, mlp, lw) -> None:
+        """self.xb[:T] -> self.y[:T] (fp32)."""
+        if mlp.kind == "moe":
+            e = mlp.moe
+            shared = None
+            if e.shared_ff:
+                act = self._view(self.act, T, e.shared_ff)
+                ops.gated_linear(self.xb[:T], lw.shared13, act, "clamped_swish", e.shared_limit)
+                shared = self.routed_ws.shared[:T]
+                ops.linear(act, lw.shared2, shared)
+                self.stats["kernel_launches"] += 2
+            ops.routed_experts(self.xb[:T], lw.router, lw.correction, lw.w13, lw.w2, self.routed_ws, self.y[:T], e.experts,
+                               e.identity, e.top, e.scale, e.ff, e.limit, shared=shared)
+            self.stats["kernel_launches"] += ops.ROUTED_LAUNCHES
+            return
+        act = self._view(self.act, T, mlp.ff)
+        if mlp.act == "relu2":
+            ops.linear(self.xb[:T], lw.up, act, relu2=True)            # squared ReLU in the GEMM's epilogue
+        else:
+            ops.gated_linear(self.xb[:T], lw.gate_up, act, mlp.act)
+        ops.linear(act, lw.down, self.y[:T])
+        self.stats["kernel_launches"] += 2
 
     def _forward_decode(self, ids, B: int, bt, lens, state_slots) -> None:
         if self.mcfg.has_state and self.num_state_slots == 0:
@@ -217,8 +333,12 @@ class LayerListRunner(ModelRunner):
         cfg = self.mcfg
         if rows is None:
             rows = self.arange_dev[:n]
-        ops.sum_layer_norm(None, self.resid32, self.w.final_norm, 1.0, cfg.norm_eps, xb_out=self.x_last[:n], rows=rows,
-                           out_scale=cfg.logit_scale)
+        if self.streams:       # sum of the streams, tanh norm
+            ops.streams_step(self.resid32, self.S, rows=rows, xb_out=self.x_last[:n],
+                             norm=(self.w.final_norm_alpha, self.w.final_norm, self.w.final_norm_b))
+        else:
+            ops.sum_layer_norm(None, self.resid32, self.w.final_norm, 1.0, cfg.norm_eps, xb_out=self.x_last[:n], rows=rows,
+                               out_scale=cfg.logit_scale)
         lg = self.logits[:n]
         ops.linear(self.x_last[:n], self.w.lm_head, lg)
         ops.sample(lg, temps, seeds, out_idx=self.out_ids[:n])

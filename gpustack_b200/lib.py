@@ -79,9 +79,9 @@ SIGNATURES = {
                               _i32, _f32, _f32, _i32, _vp]),
     "b200_attn_sink_prefill_tile": (_i32, []),
     "b200_attn_sink_prefill": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _i32, _vp, _vp,
-                                      _i64, _i32, _i32, _i32, _i32, _i32, _f32, _vp]),
+                                      _i64, _i32, _i32, _i32, _i32, _i32, _f32, _i64, _vp]),
     "b200_attn_sink_decode": (_i32, [_vp, _i32, _i64, _i32, _vp, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _i64, _i32, _i32,
-                                     _i32, _i32, _i32, _f32, _vp]),
+                                     _i32, _i32, _i32, _f32, _i64, _vp]),
     "b200_attn_prefill_tc_covers": (_i32, [_i32, _i32, _i32]),
     "b200_paged_attn_prefill_ex": (_i32, [_vp, _i64, _i32, _vp, _vp, _i32, _vp, _i32, _vp, _vp, _vp, _vp, _i32, _vp,
                                           _i32, _i32, _i32, _i32, _f32, _vp, _vp, _i64, _vp]),
@@ -91,6 +91,17 @@ SIGNATURES = {
     "b200_mlstm_state_slices": (_i32, [_i32]),
     "b200_mlstm_scan": (_i32, [_vp, _i32, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32,
                                _i32, _i32, _f32, _f32, _i32, _vp]),
+    "b200_streams_step": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _f32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
+    "b200_embed_streams": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _f32, _vp]),
+    "b200_rms_rows": (_i32, [_vp, _i32, _i64, _vp, _vp, _i64, _i32, _i32, _f32, _vp]),
+    "b200_latent_prep": (_i32, [_vp, _i32, _i64, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32,
+                                _i32, _i32, _i32, _vp, _f32, _f32, _vp]),
+    "b200_linear_simt_grouped": (_i32, [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i64, _i64,
+                                        _i64, _vp, _i32, _vp, _vp, _i32, _i64, _vp, _i32, _f32, _vp]),
+    "b200_simt_group_rows": (_i32, []),
+    "b200_moe_route_biased": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _vp]),
+    "b200_moe_combine_mixed": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _i64, _vp, _i64, _i32, _i32,
+                                      _i32, _i32, _vp]),
     "b200_mlstm_out": (_i32, [_vp, _vp, _i32, _i64, _i32, _vp, _vp, _i64, _i32, _i32, _i32, _f32, _vp]),
 }
 

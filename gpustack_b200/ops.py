@@ -524,7 +524,9 @@ def attn_sink_prefill_tile() -> int:
 
 
 def attn_sink_prefill(proj, gate_col, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out,
-                      H, G, dk, dv, scale, tile_rows: int = 0):
+                      H, G, dk, dv, scale, tile_rows: int = 0, v_ld: int = 0):
+    """v_ld: elements between value rows (0 = dv); v_cache is k_cache and v_ld == dk when the values are the
+    first dv entries of the key rows (a latent cache)."""
     _cuda(proj, k_cache, v_cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out)
     if k_cache.dtype != proj.dtype or out.dtype != proj.dtype:
         raise B200Error("attn_sink_prefill: projection, cache and output must share one element type")
@@ -532,17 +534,18 @@ def attn_sink_prefill(proj, gate_col, k_cache, v_cache, block_table, cu_q, ctx_l
                                         _p(block_table), block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq),
                                         _p(tile_q0), tile_seq.shape[0], tile_rows or attn_sink_prefill_tile(), _p(sink),
                                         _p(out), out.stride(0), H, G, dk, dv,
-                                        k_cache.shape[2], scale, _stream()), "attn_sink_prefill")
+                                        k_cache.shape[2], scale, v_ld, _stream()), "attn_sink_prefill")
     return out
 
 
-def attn_sink_decode(proj, gate_col, k_cache, v_cache, block_table, seq_lens, sink, out, H, G, dk, dv, scale):
+def attn_sink_decode(proj, gate_col, k_cache, v_cache, block_table, seq_lens, sink, out, H, G, dk, dv, scale,
+                     v_ld: int = 0):
     _cuda(proj, k_cache, v_cache, block_table, seq_lens, sink, out)
     if k_cache.dtype != proj.dtype or out.dtype != proj.dtype:
         raise B200Error("attn_sink_decode: projection, cache and output must share one element type")
     check(load().b200_attn_sink_decode(_p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(k_cache), _p(v_cache),
                                        _p(block_table), block_table.shape[1], _p(seq_lens), seq_lens.shape[0], _p(sink),
-                                       _p(out), out.stride(0), H, G, dk, dv, k_cache.shape[2], scale, _stream()),
+                                       _p(out), out.stride(0), H, G, dk, dv, k_cache.shape[2], scale, v_ld, _stream()),
           "attn_sink_decode")
     return out
 
@@ -566,4 +569,149 @@ def mlstm_out(o_raw, proj, gate_col, norm_w, out, H, dv, eps):
     _cuda(o_raw, proj, norm_w, out)
     check(load().b200_mlstm_out(_p(o_raw), _p(proj), _is_f32(proj), proj.stride(0), gate_col, _p(norm_w), _p(out),
                                 out.stride(0), o_raw.shape[0], H, dv, eps, _stream()), "mlstm_out")
+    return out
+
+
+# ------------------------------------------- residual streams, latent attention, gated / routed feed-forward
+GATED_ACTS = {"gelu_tanh": 1, "clamped_swish": 2, "silu": 3}
+
+
+def embed_streams(ids, table, X, S: int, scale: float = 1.0):
+    """X [T, S*D] fp32: every stream of row t = table[ids[t]] * scale."""
+    _cuda(ids, table, X)
+    _req(ids, torch.int32, "ids"); _req(table, torch.bfloat16, "table"); _req(X, torch.float32, "X")
+    check(load().b200_embed_streams(_p(ids), _p(table), _p(X), ids.shape[0], S, table.shape[1], table.shape[0], scale,
+                                    _stream()), "embed_streams")
+
+
+def streams_step(X, S: int, y=None, hc_write=None, mult: float = 1.0, hc_read=None, norm=None, xb_out=None, rows=None):
+    """X [T, S*D] fp32 residual streams.  y (fp32 / bf16 [T, D]) with hc_write ([in | out | mix] fp32): the streams
+    take the branch output, X_t <- sum_s mix[s, t] X_s + mult * out[t] * y.  Then u = sum_t hc_read[t] X_t (None: the
+    plain sum) and xb_out = tanh(alpha u) w + b with norm = (alpha [1] fp32, w, b).  rows: gather (no y)."""
+    _cuda(X, y, hc_write, hc_read, xb_out, rows)
+    _req(X, torch.float32, "X")
+    D = X.shape[1] // S
+    T = rows.shape[0] if rows is not None else (y.shape[0] if y is not None else X.shape[0])
+    alpha, w, b = norm if norm is not None else (None, None, None)
+    check(load().b200_streams_step(_p(y), 0 if y is None else _is_f32(y), 0 if y is None else y.stride(0), _p(X), _p(rows),
+                                   _p(hc_write), mult, _p(hc_read), _p(alpha), _p(w), _p(b), _p(xb_out),
+                                   0 if xb_out is None else _is_f32(xb_out), T, S, D, _stream()), "streams_step")
+
+
+def rms_rows(x, w, out, eps: float):
+    """out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w; x / out may be column slices of wider rows."""
+    _cuda(x, w, out)
+    if x.dtype != out.dtype or x.stride(1) != 1 or out.stride(1) != 1:
+        raise B200Error("rms_rows: one element type, contiguous rows")
+    check(load().b200_rms_rows(_p(x), _is_f32(x), x.stride(0), _p(w), _p(out), out.stride(0), x.shape[0], x.shape[1], eps,
+                               _stream()), "rms_rows")
+    return out
+
+
+def latent_prep(proj, kv_col: int, q, kv_norm_w, positions, slots, cache, qa, H, dn, dr, R, rot_dims, half_layout: bool,
+                freq, mag: float, eps: float):
+    """Latent attention's cache write and rotations (csrc/latent.cu).  proj [T, ..] holds the latent and key part at
+    kv_col; q [T, H*(dn+dr)]; cache [blocks, page, R+dr]; qa [T, H*(R+dr)] receives the rotated query parts."""
+    _cuda(proj, q, kv_norm_w, positions, slots, cache, qa, freq)
+    _req(freq, torch.float64, "freq")
+    if not (proj.dtype == q.dtype == cache.dtype == qa.dtype):
+        raise B200Error("latent_prep: projection, queries, cache and absorbed queries share one element type")
+    check(load().b200_latent_prep(_p(proj), _is_f32(proj), proj.stride(0), kv_col, _p(q), q.stride(0), _p(kv_norm_w),
+                                  _p(positions), _p(slots), _p(cache), _p(qa), qa.stride(0), proj.shape[0], H, dn, dr, R,
+                                  rot_dims, 1 if half_layout else 0, _p(freq), mag, eps, _stream()), "latent_prep")
+
+
+def simt_group_rows() -> int:
+    return load().b200_simt_group_rows()
+
+
+def linear_simt_grouped(x, w, out, M, N, K, ldx, ldw, ldy, batch=1, bsx=0, bsw=0, bsy=0, row_pair=None, top_k=1,
+                        tile_expert=None, num_tiles=None, n_real=0, w_expert=0, row_scale=None, act: int = 0,
+                        limit: float = 0.0):
+    _cuda(x, w, out, row_pair, tile_expert, num_tiles, row_scale)
+    if w.dtype != torch.bfloat16:
+        raise B200Error("linear_simt_grouped: bf16 weights")
+    check(load().b200_linear_simt_grouped(_p(x), _is_f32(x), _p(w), _p(out), _is_f32(out), M, N, K, ldx, ldw, ldy, batch,
+                                          bsx, bsw, bsy, _p(row_pair), top_k, _p(tile_expert), _p(num_tiles), n_real,
+                                          w_expert, _p(row_scale), act, limit, _stream()), "linear_simt_grouped")
+    return out
+
+
+def head_linear(x, w, out, H: int, n: int, k: int, x_head: int, out_head: int):
+    """Per-head linear: out[t, h*out_head : +n] = w[h] (n x k, contiguous) @ x[t, h*x_head : +k] for every head."""
+    return linear_simt_grouped(x, w, out, x.shape[0], n, k, x.stride(0), k, out.stride(0), batch=H, bsx=x_head, bsw=n * k,
+                               bsy=out_head)
+
+
+def _tc_gemm_ok(x, w, out, K) -> bool:
+    return (x.dtype == torch.bfloat16 and K % 64 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and (out.stride(0) * out.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and out.data_ptr() % 16 == 0)
+
+
+def gated_linear(x, w_interleaved, out, act: str, limit: float = 0.0):
+    """out = act(x @ gate.T) (*) (x @ up.T) with interleaved gate / up rows (weights._interleave_rows); the
+    activation is computed in fp32 from the fp32 accumulators and rounded once."""
+    M, K = x.shape
+    N = w_interleaved.shape[0] // 2
+    return linear_simt_grouped(x, w_interleaved, out, M, N, K, x.stride(0), w_interleaved.stride(0), out.stride(0),
+                               act=GATED_ACTS[act], limit=limit)
+
+
+def moe_route_biased(logits, correction, top_k: int, scale: float, out_ids, out_w, num_experts: int):
+    _cuda(logits, correction, out_ids, out_w)
+    _req(logits, torch.float32, "logits")
+    check(load().b200_moe_route_biased(_p(logits), logits.stride(0), _p(correction), _p(out_ids), _p(out_w),
+                                       logits.shape[0], num_experts, top_k, scale, _stream()), "moe_route_biased")
+
+
+class RoutedWorkspace:
+    """Device buffers of one routed feed-forward (sized for max_tokens tokens, shared by every layer): pair
+    bookkeeping of moe_align with 64-row tiles, the experts' hidden rows and their weighted outputs (fp32)."""
+
+    def __init__(self, max_tokens: int, top_k: int, e_total: int, D: int, ff: int, act_dtype, device):
+        self.bx = simt_group_rows()
+        n_pairs = max_tokens * top_k
+        self.capacity = moe_capacity_rows(n_pairs, e_total, self.bx)
+        i32 = lambda *s: torch.empty(*s, dtype=torch.int32, device=device)   # noqa: E731
+        self.logits = torch.empty(max_tokens, e_total, dtype=torch.float32, device=device)
+        self.topk_ids, self.topk_w = i32(n_pairs), torch.empty(n_pairs, dtype=torch.float32, device=device)
+        self.pair_row, self.row_pair = i32(n_pairs), i32(self.capacity)
+        self.row_weight = torch.empty(self.capacity, dtype=torch.float32, device=device)
+        self.tile_expert, self.num_tiles = i32(self.capacity // self.bx + 1), torch.zeros(2, dtype=torch.int32, device=device)
+        self.act = torch.empty(self.capacity * ff, dtype=act_dtype, device=device)
+        self.yp = torch.empty(self.capacity, D, dtype=torch.float32, device=device)
+        self.shared = torch.empty(max_tokens, D, dtype=torch.float32, device=device)
+
+
+ROUTED_LAUNCHES = 6
+
+
+def routed_experts(x, router, correction, w13, w2, ws: RoutedWorkspace, out, n_real: int, n_identity: int, top_k: int,
+                   scale: float, ff: int, limit: float, shared=None):
+    """out[t] (fp32) = sum over the top_k chosen router outputs of weight * expert(x[t]) (identity experts return
+    x[t]) + shared[t].  router [n_real + n_identity, D]; w13 [n_real * 2 ff, D] interleaved; w2 [n_real * D, ff];
+    shared: the shared expert's output rows (fp32) or None.  Six launches, no host synchronisation."""
+    T, D = x.shape
+    E = n_real + n_identity
+    n_pairs = T * top_k
+    cap = moe_capacity_rows(n_pairs, E, ws.bx)
+    if cap > ws.capacity:
+        raise B200Error(f"routed_experts: {T} tokens exceed the workspace ({ws.capacity} rows)")
+    L, st = load(), _stream()
+    lg = ws.logits[:T]
+    linear(x, router, lg)                                           # fp32 logits
+    moe_route_biased(lg, correction, top_k, scale, ws.topk_ids, ws.topk_w, E)
+    check(L.b200_moe_align(_p(ws.topk_ids), _p(ws.topk_w), n_pairs, E, ws.bx, cap, _p(ws.pair_row), _p(ws.row_pair),
+                           _p(ws.row_weight), _p(ws.tile_expert), _p(ws.num_tiles), st), "moe_align")
+    act = ws.act[:cap * ff].view(cap, ff)
+    if n_real:
+        linear_simt_grouped(x, w13, act, cap, ff, D, x.stride(0), w13.stride(0), ff, row_pair=ws.row_pair, top_k=top_k,
+                            tile_expert=ws.tile_expert, num_tiles=ws.num_tiles, n_real=n_real, w_expert=2 * ff * w13.stride(0),
+                            act=GATED_ACTS["clamped_swish"], limit=limit)
+        linear_simt_grouped(act, w2, ws.yp, cap, D, ff, ff, w2.stride(0), D, tile_expert=ws.tile_expert,
+                            num_tiles=ws.num_tiles, n_real=n_real, w_expert=D * w2.stride(0), row_scale=ws.row_weight)
+    check(L.b200_moe_combine_mixed(_p(ws.yp), 1, D, _p(ws.pair_row), _p(ws.topk_ids), _p(ws.topk_w), _p(x), _is_f32(x),
+                                   x.stride(0), _p(shared), 0 if shared is None else shared.stride(0), _p(out), out.stride(0),
+                                   T, D, top_k, n_real, st), "moe_combine_mixed")
     return out

@@ -350,6 +350,31 @@ class LayerListLayer:
     norm2: Optional[torch.Tensor] = None
     up: Optional[torch.Tensor] = None
     down: Optional[torch.Tensor] = None
+    # tanh norm: bias vector and the scalar alpha (fp32 [1]) of norm1 / norm2
+    norm1_b: Optional[torch.Tensor] = None
+    norm1_alpha: Optional[torch.Tensor] = None
+    norm2_b: Optional[torch.Tensor] = None
+    norm2_alpha: Optional[torch.Tensor] = None
+    # residual streams: per sublayer ONE fp32 vector [in: s | out: s | mix: s*s (from, to)]
+    hc1: Optional[torch.Tensor] = None
+    hc2: Optional[torch.Tensor] = None
+    # latent attention: proj rows = [q: H*(dim+rot_dim)  or  query latent: q_rank | latent: kv_rank | key part: rot_dim]
+    q_lat_norm: Optional[torch.Tensor] = None    # [q_rank]
+    uq: Optional[torch.Tensor] = None            # [H*(dim+rot_dim), q_rank]
+    kv_norm: Optional[torch.Tensor] = None       # [kv_rank]
+    uk_t: Optional[torch.Tensor] = None          # [H, kv_rank, dim]: W_uk of each head transposed (query absorption)
+    uv: Optional[torch.Tensor] = None            # [H*vdim, kv_rank]
+    rot_freq: Optional[torch.Tensor] = None      # fp64 [dims/2]: angular frequency of every rotated pair
+    rot_mag: float = 1.0                         # factor on cos and sin (frequency-scaled rotations)
+    # gated feed-forward: gate_up rows interleaved (2i = gate_i, 2i+1 = up_i), `up` above is unused
+    gate_up: Optional[torch.Tensor] = None       # [2 ff, D]
+    # routed feed-forward
+    router: Optional[torch.Tensor] = None        # [experts + identity, D]
+    correction: Optional[torch.Tensor] = None    # fp32 [experts + identity]
+    w13: Optional[torch.Tensor] = None           # [experts * 2 ff, D], per expert interleaved gate / up rows
+    w2: Optional[torch.Tensor] = None            # [experts * D, ff]
+    shared13: Optional[torch.Tensor] = None      # [2 shared_ff, D]
+    shared2: Optional[torch.Tensor] = None       # [D, shared_ff]
 
 
 @dataclass
@@ -360,16 +385,43 @@ class LayerListWeights:
     lm_head: torch.Tensor
     vocab_start: int = 0
     vocab_end: int = 0
+    final_norm_b: Optional[torch.Tensor] = None
+    final_norm_alpha: Optional[torch.Tensor] = None
 
 
 def layer_list_tensor_shapes(cfg) -> Dict[str, tuple]:
     """Checkpoint tensor names and shapes of a layer-list model (linear weights are [out, in])."""
     D = cfg.hidden_size
     shapes: Dict[str, tuple] = {"embed": (cfg.vocab_size, D), "final.norm": (D,), "head": (cfg.vocab_size, D)}
+    tanh = getattr(cfg, "norm", "layernorm") == "tanh"
+    S = getattr(cfg, "streams", 0)
+
+    def norm_shapes(name):
+        shapes[name] = (D,)
+        if tanh:
+            shapes[name + ".b"] = (D,)
+            shapes[name + ".alpha"] = ()
+
+    if tanh:
+        norm_shapes("final.norm")
     for l, layer in enumerate(cfg.layers):
         p, m = f"l{l}.", layer.mixer
-        shapes[p + "norm1"] = (D,)
-        if m.kind == "attention":
+        norm_shapes(p + "norm1")
+        for q in ((1, 2) if layer.mlp is not None else (1,)) if S else ():
+            shapes[p + f"hc{q}.in"], shapes[p + f"hc{q}.out"], shapes[p + f"hc{q}.mix"] = (S,), (S,), (S, S)
+        if m.kind == "latent_attention":
+            if m.q_rank:
+                shapes[p + "mix.dq"], shapes[p + "mix.dq.norm"] = (m.q_rank, D), (m.q_rank,)
+                shapes[p + "mix.uq"] = (m.q_width, m.q_rank)
+            else:
+                shapes[p + "mix.q"] = (m.q_width, D)
+            shapes[p + "mix.dkv"], shapes[p + "mix.dkv.norm"] = (m.cache_width, D), (m.kv_rank,)
+            shapes[p + "mix.uk"] = (m.heads * m.dim, m.kv_rank)
+            shapes[p + "mix.uv"] = (m.out_width, m.kv_rank)
+            if m.sink:
+                shapes[p + "mix.sink"] = (m.heads,)
+            shapes[p + "mix.o"] = (D, m.out_width)
+        elif m.kind == "attention":
             shapes[p + "mix.q"] = (m.q_width, D)
             if m.qkv_bias:
                 shapes[p + "mix.q.b"] = (m.q_width,)
@@ -397,10 +449,28 @@ def layer_list_tensor_shapes(cfg) -> Dict[str, tuple]:
                 shapes[p + "mix." + n] = (m.heads, D)
                 shapes[p + "mix." + n + ".b"] = (m.heads,)
         if layer.mlp is not None:
-            shapes[p + "norm2"] = (D,)
+            norm_shapes(p + "norm2")
+            if layer.mlp.kind == "moe":
+                e = layer.mlp.moe
+                for i in range(e.experts):
+                    shapes[p + f"mlp.e{i}.gate"] = shapes[p + f"mlp.e{i}.up"] = (e.ff, D)
+                    shapes[p + f"mlp.e{i}.down"] = (D, e.ff)
+                shapes[p + "mlp.router"] = (e.experts + e.identity, D)
+                shapes[p + "mlp.correction"] = (e.experts + e.identity,)
+                if e.shared_ff:
+                    shapes[p + "mlp.shared.gate"] = shapes[p + "mlp.shared.up"] = (e.shared_ff, D)
+                    shapes[p + "mlp.shared.down"] = (D, e.shared_ff)
+                continue
+            if layer.mlp.act != "relu2":
+                shapes[p + "mlp.gate"] = (layer.mlp.ff, D)
             shapes[p + "mlp.up"] = (layer.mlp.ff, D)
             shapes[p + "mlp.down"] = (D, layer.mlp.ff)
     return shapes
+
+
+def _interleave_rows(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[n, K] gate and up rows -> [2n, K] with row 2i = gate_i, row 2i+1 = up_i (the layout of the gated epilogues)."""
+    return torch.stack((gate, up), dim=1).reshape(2 * gate.shape[0], gate.shape[1]).contiguous()
 
 
 def load_layer_list(cfg, get: Callable[[str], torch.Tensor], device: str) -> LayerListWeights:
@@ -417,10 +487,34 @@ def load_layer_list(cfg, get: Callable[[str], torch.Tensor], device: str) -> Lay
     def cat(names):
         return torch.cat([g(n) for n in names], dim=0).contiguous()
 
+    def f32(name: str) -> torch.Tensor:
+        return g(name).to(torch.float32).reshape(-1).contiguous()
+
+    tanh = getattr(cfg, "norm", "layernorm") == "tanh"
+    S = getattr(cfg, "streams", 0)
+
+    def hyper(prefix: str) -> torch.Tensor:
+        if not S:        # one plain residual stream: read it, keep it, add the branch
+            return torch.ones(3, dtype=torch.float32, device=device)
+        return torch.cat([f32(prefix + ".in"), f32(prefix + ".out"), f32(prefix + ".mix")]).contiguous()
+
     layers = []
     for l, layer in enumerate(cfg.layers):
         p, m = f"l{l}.", layer.mixer
-        if m.kind == "attention":
+        if m.kind == "latent_attention":
+            first = g(p + "mix.dq") if m.q_rank else g(p + "mix.q")
+            lw = LayerListLayer(norm1=g(p + "norm1"), proj=torch.cat([first, g(p + "mix.dkv")], dim=0).contiguous(),
+                                o=g(p + "mix.o"))
+            if m.q_rank:
+                lw.q_lat_norm, lw.uq = g(p + "mix.dq.norm"), g(p + "mix.uq")
+            lw.kv_norm = g(p + "mix.dkv.norm")
+            lw.uk_t = g(p + "mix.uk").view(m.heads, m.dim, m.kv_rank).transpose(1, 2).contiguous()
+            lw.uv = g(p + "mix.uv")
+            if m.sink:
+                lw.sink = f32(p + "mix.sink")
+            freqs, mag = m.rot.frequencies()
+            lw.rot_freq, lw.rot_mag = torch.tensor(list(freqs), dtype=torch.float64).to(device), float(mag)
+        elif m.kind == "attention":
             own = m.kv_from is None
             names = ["q"] + (["k", "v"] if own else []) + (["g"] if m.gate else [])
             lw = LayerListLayer(norm1=g(p + "norm1"), proj=cat([p + "mix." + n for n in names]), o=g(p + "mix.o"))
@@ -435,11 +529,35 @@ def load_layer_list(cfg, get: Callable[[str], torch.Tensor], device: str) -> Lay
             lw = LayerListLayer(norm1=g(p + "norm1"), proj=cat([p + "mix." + n for n in "qkvg"]), o=g(p + "mix.o"),
                                 gates=cat([p + "mix.i", p + "mix.f"]), gate_bias=cat([p + "mix.i.b", p + "mix.f.b"]),
                                 out_norm=g(p + "mix.norm"))
+        if tanh:
+            lw.norm1_b, lw.norm1_alpha = g(p + "norm1.b"), f32(p + "norm1.alpha")
+        if getattr(cfg, "residual", "post_ln") == "streams":
+            lw.hc1 = hyper(p + "hc1")
         if layer.mlp is not None:
-            lw.norm2, lw.up, lw.down = g(p + "norm2"), g(p + "mlp.up"), g(p + "mlp.down")
+            lw.norm2 = g(p + "norm2")
+            if tanh:
+                lw.norm2_b, lw.norm2_alpha = g(p + "norm2.b"), f32(p + "norm2.alpha")
+            if getattr(cfg, "residual", "post_ln") == "streams":
+                lw.hc2 = hyper(p + "hc2")
+            if layer.mlp.kind == "moe":
+                e = layer.mlp.moe
+                lw.router, lw.correction = g(p + "mlp.router"), f32(p + "mlp.correction")
+                lw.w13 = torch.cat([_interleave_rows(g(p + f"mlp.e{i}.gate"), g(p + f"mlp.e{i}.up"))
+                                    for i in range(e.experts)], dim=0).contiguous()
+                lw.w2 = torch.cat([g(p + f"mlp.e{i}.down") for i in range(e.experts)], dim=0).contiguous()
+                if e.shared_ff:
+                    lw.shared13 = _interleave_rows(g(p + "mlp.shared.gate"), g(p + "mlp.shared.up"))
+                    lw.shared2 = g(p + "mlp.shared.down")
+            elif layer.mlp.act == "relu2":
+                lw.up, lw.down = g(p + "mlp.up"), g(p + "mlp.down")
+            else:
+                lw.gate_up, lw.down = _interleave_rows(g(p + "mlp.gate"), g(p + "mlp.up")), g(p + "mlp.down")
         layers.append(lw)
-    return LayerListWeights(embed=g("embed"), layers=layers, final_norm=g("final.norm"), lm_head=g("head"),
-                            vocab_start=0, vocab_end=cfg.vocab_size)
+    out = LayerListWeights(embed=g("embed"), layers=layers, final_norm=g("final.norm"), lm_head=g("head"),
+                           vocab_start=0, vocab_end=cfg.vocab_size)
+    if tanh:
+        out.final_norm_b, out.final_norm_alpha = g("final.norm.b"), f32("final.norm.alpha")
+    return out
 
 
 def load_layer_list_dir(cfg, model_path: str, device: str) -> LayerListWeights:
@@ -463,9 +581,19 @@ def random_layer_list_state(cfg, seed: int = 0, device: str = "cpu") -> Dict[str
     gen = torch.Generator(device=device).manual_seed(seed)
     out: Dict[str, torch.Tensor] = {}
     for name, shape in layer_list_tensor_shapes(cfg).items():
-        x = torch.randn(*shape, generator=gen, device=device, dtype=torch.float32)
+        x = torch.randn(tuple(shape), generator=gen, device=device, dtype=torch.float32)
         leaf = name.split(".", 1)[1] if name[0] == "l" and name[1].isdigit() else name
-        if leaf.endswith("norm") or leaf in ("norm1", "norm2"):
+        if leaf.endswith(".alpha"):
+            x = 0.5 + 0.1 * x
+        elif leaf.endswith("norm.b") or leaf in ("norm1.b", "norm2.b"):
+            x = 0.1 * x
+        elif leaf.endswith(".mix") and leaf.startswith("hc"):
+            x = torch.eye(shape[0], device=device) * 0.8 + 0.15 * x
+        elif leaf.startswith("hc"):
+            x = 0.7 + 0.2 * x
+        elif leaf == "mlp.correction":
+            x = 0.05 * x
+        elif leaf.endswith("norm") or leaf in ("norm1", "norm2"):
             x = 1.0 + 0.2 * x
         elif leaf == "mix.f.b":
             x = 3.0 + x
@@ -476,7 +604,7 @@ def random_layer_list_state(cfg, seed: int = 0, device: str = "cpu") -> Dict[str
         elif leaf == "embed":
             pass
         else:
-            x = x / (shape[-1] ** 0.5)
+            x = x / (shape[-1] ** 0.5) if len(shape) else x
         out[name] = x.to(BF16)
     return out
 

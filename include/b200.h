@@ -263,17 +263,19 @@ int b200_attn_prep(void* proj, int f32, int64_t ld, const void* bias, const void
 int b200_attn_sink_prefill_tile(void);
 /* Causal attention of prompt portions over the paged cache, tiles of tile_rows rows (a multiple of
  * b200_attn_sink_prefill_tile()); sink [H] fp32 or NULL; gate_col >= 0:
- * the output is multiplied by sigmoid(proj[t, gate_col + h*dv + d]). */
+ * the output is multiplied by sigmoid(proj[t, gate_col + h*dv + d]).  v_ld: elements between value rows
+ * (0 = dv); v_cache == k_cache with v_ld == dk reads the values from the first dv entries of the key rows. */
 int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
                            const void* v_cache, const int32_t* block_table, int max_blocks,
                            const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
                            const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
-                           int64_t ldo, int H, int G, int dk, int dv, int page, float scale, void* stream);
+                           int64_t ldo, int H, int G, int dk, int dv, int page, float scale, int64_t v_ld,
+                           void* stream);
 /* The same for one new row per sequence (row b of proj / out sees keys [0, seq_lens[b])). */
 int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int gate_col, const void* k_cache,
                           const void* v_cache, const int32_t* block_table, int max_blocks,
                           const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo, int H,
-                          int G, int dk, int dv, int page, float scale, void* stream);
+                          int G, int dk, int dv, int page, float scale, int64_t v_ld, void* stream);
 /* The tensor-core kernels of the Llama-class models with the same two options, for mixers whose key and
  * value widths are equal and a tile size (decode: D 64 / 128; prefill: D 128, group of 4 or 8, tiles of
  * b200_attn_prefill_tile rows): sink [Hq] fp32 or NULL joins the softmax denominator, gate (bf16,
@@ -310,6 +312,42 @@ int b200_mlstm_scan(const void* proj, int f32, int64_t ld, int q_col, int k_col,
 int b200_mlstm_out(const float* o_raw, const void* proj, int f32, int64_t ld, int gate_col,
                    const void* norm_w, void* out, int64_t ldo, int T, int H, int dv, float eps,
                    void* stream);
+
+/* ---- latent attention, residual streams, gated / routed feed-forward (layer-list decoders) ------------- */
+/* X [T][S][D] fp32 streams.  y != NULL: X_t <- sum_s mix[s][t] X_s + mult * out[t] * y  (hc_write = [in: S | out: S |
+ * mix: S*S, (from, to)]).  Then u = sum_t hc_read[t] X_t (hc_read NULL: the plain sum) and, when xb_out != NULL,
+ * xb_out[r] = tanh(alpha[0] * u) * w + b.  rows != NULL (only without y): row r reads X[rows[r]]. */
+int b200_streams_step(const void* y, int y_f32, int64_t ldy, float* X, const int32_t* rows, const float* hc_write,
+                      float mult, const float* hc_read, const float* alpha, const void* w, const void* b,
+                      void* xb_out, int xb_f32, int T, int S, int D, void* stream);
+/* X[t][s] = table[ids[t]] * scale for every stream s. */
+int b200_embed_streams(const int32_t* ids, const void* table, float* X, int T, int S, int D, int V, float scale,
+                       void* stream);
+/* out[t, :n] = x[t, :n] / sqrt(mean(x^2) + eps) * w, rows ldx / ldo apart. */
+int b200_rms_rows(const void* x, int f32, int64_t ldx, const void* w, void* out, int64_t ldo, int T, int n, float eps,
+                  void* stream);
+/* Per token: RMS norm of the latent proj[t, kv_col : kv_col + R] into cache row slots[t] ([.., R + dr]), the
+ * rotated key part proj[t, kv_col + R : + dr] behind it, and every head's rotated query part q[t, h, dn : dn + dr]
+ * into qa[t, h, R : R + dr].  Rotation of the first `dims` entries at positions[t] with freq[dims / 2] (fp64),
+ * pairs (2i, 2i+1) or, half_layout, (i, i + dims/2); cos and sin times mag. */
+int b200_latent_prep(const void* proj, int f32, int64_t ld, int kv_col, const void* q, int64_t ldq,
+                     const void* kv_norm_w, const int32_t* positions, const int32_t* slots, void* cache, void* qa,
+                     int64_t ldqa, int T, int H, int dn, int dr, int R, int dims, int half_layout, const double* freq,
+                     float mag, float eps, void* stream);
+/* Batched / grouped / gated linear on the CUDA cores (see gemm_simt_grouped.cu).  act: 0 plain, 1 gelu_tanh(g) u,
+ * 2 clamped g sigmoid(1.702 g) (u + 1) with `limit`, 3 silu(g) u; act != 0: W rows interleaved gate / up, N pairs. */
+int b200_linear_simt_grouped(const void* X, int x_f32, const void* W, void* Y, int y_f32, int M, int N, int K,
+                             int64_t ldx, int64_t ldw, int64_t ldy, int batch, int64_t bsx, int64_t bsw, int64_t bsy,
+                             const int32_t* row_pair, int top_k, const int32_t* tile_expert, const int32_t* num_tiles,
+                             int n_real, int64_t w_expert, const float* row_scale, int act, float limit, void* stream);
+int b200_simt_group_rows(void);
+/* Softmax over E fp32 router outputs, top K of score + correction, weights score / (sum + 1e-20) * scale. */
+int b200_moe_route_biased(const float* logits, int64_t ld, const float* correction, int32_t* topk_ids, float* topk_w,
+                          int T, int E, int K, float scale, void* stream);
+/* out[t] = sum_j (topk_ids[t, j] < n_real ? yp[pair_row[t K + j]] : topk_w[t, j] * x[t]) (+ shared[t]); fp32 out. */
+int b200_moe_combine_mixed(const void* yp, int p_f32, int64_t ldp, const int32_t* pair_row, const int32_t* topk_ids,
+                           const float* topk_w, const void* x, int x_f32, int64_t ldx, const void* shared, int64_t lds,
+                           float* out, int64_t ldo, int T, int D, int K, int n_real, void* stream);
 
 #ifdef __cplusplus
 }
