@@ -212,3 +212,78 @@ def forward(cfg: dict, state: Dict[str, torch.Tensor], tokens: List[int], dtype=
             layer_outputs.append(X.sum(dim=0))
     x = X.sum(dim=0)
     return norm(x, "final.norm") @ st["head"].T
+
+
+# ------------------------------------------------------------------------------ random models for tests
+def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
+    D, S = cfg["width"], int(cfg.get("streams", 0) or 0)
+    sh: Dict[str, tuple] = {"embed": (cfg["vocab"], D), "head": (cfg["vocab"], D)}
+
+    def norm(name):
+        sh[name], sh[name + ".b"], sh[name + ".alpha"] = (D,), (D,), ()
+
+    norm("final.norm")
+    for l, layer in enumerate(cfg["layers"]):
+        p, m = f"l{l}.", layer["mixer"]
+        H, dn, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+        norm(p + "norm1")
+        if layer["type"] == "latent_attention_2":
+            sh[p + "mix.dq"], sh[p + "mix.dq.norm"], sh[p + "mix.uq"] = (m["q_rank"], D), (m["q_rank"],), (H * (dn + dr), m["q_rank"])
+        else:
+            sh[p + "mix.q"], sh[p + "mix.sink"] = (H * (dn + dr), D), (H,)
+        sh[p + "mix.dkv"], sh[p + "mix.dkv.norm"] = (R + dr, D), (R,)
+        sh[p + "mix.uk"], sh[p + "mix.uv"], sh[p + "mix.o"] = (H * dn, R), (H * dv, R), (D, H * dv)
+        subs = [1]
+        mlp = layer.get("mlp")
+        if mlp is not None:
+            subs.append(2)
+            norm(p + "norm2")
+            if mlp["kind"] == "dense":
+                sh[p + "mlp.gate"] = sh[p + "mlp.up"] = (mlp["ff"], D)
+                sh[p + "mlp.down"] = (D, mlp["ff"])
+            else:
+                r = mlp["router"]
+                n_out = r["experts"] + int(r.get("identity", 0) or 0)
+                for e in range(r["experts"]):
+                    sh[p + f"mlp.e{e}.gate"] = sh[p + f"mlp.e{e}.up"] = (mlp["expert"]["ff"], D)
+                    sh[p + f"mlp.e{e}.down"] = (D, mlp["expert"]["ff"])
+                sh[p + "mlp.router"], sh[p + "mlp.correction"] = (n_out, D), (n_out,)
+                if mlp.get("shared"):
+                    sh[p + "mlp.shared.gate"] = sh[p + "mlp.shared.up"] = (mlp["shared"]["ff"], D)
+                    sh[p + "mlp.shared.down"] = (D, mlp["shared"]["ff"])
+        for q in subs if S else []:
+            sh[p + f"hc{q}.in"], sh[p + f"hc{q}.out"], sh[p + f"hc{q}.mix"] = (S,), (S,), (S, S)
+    return sh
+
+
+def random_weights(cfg: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Seeded bf16 weights with the design's tensor names, scaled so that every mechanism matters: gate and up
+    projections large enough to reach the clamp, router rows that spread the choice, corrections that overturn
+    some of it, sinks of order one, stream weights away from 0 / 1."""
+    g = torch.Generator().manual_seed(seed)
+    out: Dict[str, torch.Tensor] = {}
+    for name, shape in tensor_shapes(cfg).items():
+        x = torch.randn(tuple(shape), generator=g)
+        leaf = name.split(".", 1)[1] if name[0] == "l" and name[1].isdigit() else name
+        if leaf.endswith(".alpha"):
+            x = 0.6 + 0.1 * x
+        elif leaf.endswith("norm.b") or leaf in ("norm1.b", "norm2.b"):
+            x = 0.2 * x
+        elif leaf.endswith("norm") or leaf in ("norm1", "norm2"):
+            x = 1.0 + 0.2 * x
+        elif leaf.startswith("hc") and leaf.endswith(".mix"):
+            x = 0.7 * torch.eye(shape[0]) + 0.2 * x
+        elif leaf.startswith("hc"):
+            x = 0.8 + 0.3 * x
+        elif leaf == "mix.sink":
+            x = 1.5 * x
+        elif leaf == "mlp.correction":
+            x = 0.1 * x
+        elif leaf == "mlp.router":
+            x = 3.0 * x / math.sqrt(shape[-1])
+        elif leaf.endswith(".gate") or leaf.endswith(".up"):
+            x = 2.0 * x / math.sqrt(shape[-1])
+        elif leaf != "embed":
+            x = x / math.sqrt(shape[-1])
+        out[name] = x.to(torch.bfloat16)
+    return out
