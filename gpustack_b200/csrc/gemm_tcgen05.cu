@@ -23,6 +23,7 @@
 #include "../../include/b200.h"
 
 #include <stdlib.h>
+#include <string.h>
 
 namespace b200 {
 
@@ -91,6 +92,36 @@ struct DirectOut {
   int64_t ldy;
 };
 
+// Gate activations of the EPI 1 epilogue (bits 2-3 of the flags word; bits 8-31 carry the upper 24 bits of the fp32
+// clamp bound, more than the bf16 output keeps):
+//   0  silu(g) * u with g, u and silu(g) each rounded to bf16 first (the unfused reference path's roundings),
+//   1  gelu_tanh(g) * u,                                   computed in fp32 from the fp32 accumulators,
+//   2  g' sigmoid(1.702 g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit), likewise.
+__device__ __forceinline__ float gated_pair(float g, float up, int gact, float limit) {
+  if (gact == 1) {
+    const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.0f + tanhf(z)) * up;
+  }
+  if (gact == 2) {
+    g = fminf(g, limit);
+    up = fminf(fmaxf(up, -limit), limit);
+    return g / (1.0f + __expf(-1.702f * g)) * (up + 1.0f);
+  }
+  g = round_bf16(g);
+  up = round_bf16(up);
+  return round_bf16(g / (1.f + __expf(-g))) * up;
+}
+
+__host__ __device__ inline int gated_flags(int gact, float limit) {
+#ifdef __CUDA_ARCH__
+  const uint32_t u = __float_as_uint(limit);
+#else
+  uint32_t u;
+  memcpy(&u, &limit, 4);
+#endif
+  return (int)((((uint32_t)gact & 3u) << 2) | ((u + 0x80u) & 0xffffff00u));
+}
+
 template <int BLOCK_X, int EPI, int FP8 = 0>
 __device__ __forceinline__ void epilogue_store_tile(uint32_t t_addr, const CUtensorMap* tmap_y, uint8_t* stg,
                                                     int& which, int n0, int m_base, int split, int M, int N,
@@ -99,6 +130,8 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_addr, const CUten
   constexpr int CH = BLOCK_X >= 32 ? 32 : 16;
   // out_f32 carries two flags: bit 0 = fp32 output, bit 1 = squared-ReLU activation before the store
   const bool relu2 = (out_f32 & 2) != 0;
+  const int gact = (out_f32 >> 2) & 3;
+  const float glimit = __uint_as_float((uint32_t)out_f32 & 0xffffff00u);
   out_f32 &= 1;
 #pragma unroll 1
   for (int c0 = 0; c0 < BLOCK_X; c0 += CH) {
@@ -136,11 +169,10 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_addr, const CUten
         for (int j = 0; j < CH; j += 2) {
           const uint32_t send = odd ? r[j] : r[j + 1];
           const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 1);
-          const float g = round_bf16(__uint_as_float(odd ? recv : r[j]));
-          const float up = round_bf16(__uint_as_float(odd ? r[j + 1] : recv));
-          const float sg = round_bf16(g / (1.f + __expf(-g)));
+          const float g = __uint_as_float(odd ? recv : r[j]);
+          const float up = __uint_as_float(odd ? r[j + 1] : recv);
           const int m = m_base + c0 + j + (odd ? 1 : 0);
-          if (n < N && m < M) dst[(size_t)(j + (odd ? 1 : 0)) * dir.ldy] = __float2bfloat16_rn(sg * up);
+          if (n < N && m < M) dst[(size_t)(j + (odd ? 1 : 0)) * dir.ldy] = __float2bfloat16_rn(gated_pair(g, up, gact, glimit));
         }
       } else if (n < N) {
         const size_t off = ((size_t)split * M + (size_t)(m_base + c0)) * dir.ldy + n;
@@ -164,10 +196,9 @@ __device__ __forceinline__ void epilogue_store_tile(uint32_t t_addr, const CUten
         // even lane (gate row) computes token j, odd lane (up row) computes token j+1
         const uint32_t send = odd ? r[j] : r[j + 1];
         const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 1);
-        const float g = round_bf16(__uint_as_float(odd ? recv : r[j]));
-        const float up = round_bf16(__uint_as_float(odd ? r[j + 1] : recv));
-        const float sg = round_bf16(g / (1.f + __expf(-g)));
-        const bf16 v = __float2bfloat16_rn(sg * up);
+        const float g = __uint_as_float(odd ? recv : r[j]);
+        const float up = __uint_as_float(odd ? r[j + 1] : recv);
+        const bf16 v = __float2bfloat16_rn(gated_pair(g, up, gact, glimit));
         st_shared_u16(col + (uint32_t)(j + (odd ? 1 : 0)) * 32u, *reinterpret_cast<const uint16_t*>(&v));
       }
     } else if (out_f32) {
@@ -592,8 +623,8 @@ gemm_bf16_grouped_2sm_kernel(const __grid_constant__ CUtensorMap tmap_w,
                              const __grid_constant__ CUtensorMap tmap_y, int M, int N, int K, int n_tiles,
                              int m_tiles, int group_m, const float* __restrict__ row_scale,
                              const int32_t* __restrict__ tile_expert,
-                             const int32_t* __restrict__ num_m_tiles, DirectOut dir) {
-  gemm_2sm_body<BLOCK_X, EPI, 0, 1>(tmap_w, tmap_x, tmap_y, M, N, K, 0, 1, n_tiles, m_tiles, group_m,
+                             const int32_t* __restrict__ num_m_tiles, DirectOut dir, int out_flags) {
+  gemm_2sm_body<BLOCK_X, EPI, 0, 1>(tmap_w, tmap_x, tmap_y, M, N, K, out_flags, 1, n_tiles, m_tiles, group_m,
                                     row_scale, nullptr, 0, dir, GroupInfo{tile_expert, num_m_tiles});
 }
 
@@ -911,6 +942,30 @@ extern "C" int b200_gemm_bf16_silu_mul(const void* X, const void* W, void* Y, in
   }
 }
 
+// act(x gate^T) (*) (x up^T) over interleaved gate / up rows, bf16 out [M, N/2]; act / limit as gated_pair() above.
+extern "C" int b200_gemm_bf16_gated(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx,
+                                    int64_t ldw, int64_t ldy, int act, float limit, void* stream) {
+  B200_REQUIRE(M >= 0 && N > 0 && K > 0 && N % 2 == 0, "gemm_gated: bad shape M=%d N=%d K=%d", M, N, K);
+  B200_REQUIRE(K % kBlockK == 0, "gemm_gated: K=%d must be a multiple of %d", K, kBlockK);
+  B200_REQUIRE(ldx >= K && ldw >= K && ldy >= N / 2, "gemm_gated: leading dimensions too small");
+  B200_REQUIRE(act >= 0 && act <= 2, "gemm_gated: unknown activation %d", act);
+  if (M == 0) return B200_OK;
+  const DeviceInfo& d = device_info();
+  if (!d.valid || d.cc_major != 10) {
+    b200_set_error("gemm: tcgen05 kernel needs an sm_100 device (found cc %d.%d)", d.cc_major, d.cc_minor);
+    return B200_ERR_UNSUPPORTED;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  const int fl = gated_flags(act, limit);
+  switch (plan_block_x(M, N, 1)) {
+    case 16: return launch_gemm<16, 1>(X, W, Y, M, N, K, ldx, ldw, ldy, fl, 1, s);
+    case 32: return launch_gemm<32, 1>(X, W, Y, M, N, K, ldx, ldw, ldy, fl, 1, s);
+    case 64: return launch_gemm<64, 1>(X, W, Y, M, N, K, ldx, ldw, ldy, fl, 1, s);
+    case 128: return launch_gemm<128, 1>(X, W, Y, M, N, K, ldx, ldw, ldy, fl, 1, s);
+    default: return launch_gemm<256, 1>(X, W, Y, M, N, K, ldx, ldw, ldy, fl, 1, s);
+  }
+}
+
 extern "C" int b200_gemm_bf16(const void* X, const void* W, void* Y, int M, int N, int K,
                               int64_t ldx, int64_t ldw, int64_t ldy, int out_f32, int splits,
                               void* stream) {
@@ -962,7 +1017,7 @@ namespace b200 {
 template <int BLOCK_X, int EPI>
 static int launch_gemm_grouped(const void* X, const void* W, void* Y, int M, int N, int K, int E, int64_t ldx,
                                int64_t ldw, int64_t ldy, const float* row_scale, const int32_t* tile_expert,
-                               const int32_t* num_m_tiles, cudaStream_t stream) {
+                               const int32_t* num_m_tiles, cudaStream_t stream, int out_flags = 0) {
   using Cfg = Gemm2Cfg<BLOCK_X>;
   auto kernel = gemm_bf16_grouped_2sm_kernel<BLOCK_X, EPI>;
   static bool attr_set = false;
@@ -981,7 +1036,7 @@ static int launch_gemm_grouped(const void* X, const void* W, void* Y, int M, int
   if (rc) return rc;
   CUtensorMap ty;
   DirectOut dir;
-  rc = make_out_tmap<BLOCK_X, EPI>(&ty, Y, M, N, ldy, 0, 1, &dir);
+  rc = make_out_tmap<BLOCK_X, EPI>(&ty, Y, M, N, ldy, out_flags, 1, &dir);
   if (rc) return rc;
   const int n_tiles = (N + kBlockW - 1) / kBlockW;
   const int m_tiles = (M + BLOCK_X - 1) / BLOCK_X;      // capacity; the kernel clamps to the tiles in use
@@ -991,7 +1046,7 @@ static int launch_gemm_grouped(const void* X, const void* W, void* Y, int M, int
   const int group_m = gemm_group_m(m_tiles, K);
   cudaError_t e = launch_pdl_cls(kPdlMoe, kernel, dim3(clusters * 2), dim3(kGemmThreads), (size_t)Cfg::kSmemBytes,
                                  stream, 2, tw, tx, ty, M, N, K, n_tiles, m_tiles, group_m, row_scale,
-                                 tile_expert, num_m_tiles, dir);
+                                 tile_expert, num_m_tiles, dir, out_flags);
   if (e != cudaSuccess) {
     b200_set_error("b200_moe_grouped_gemm: launch failed: %s", cudaGetErrorString(e));
     (void)cudaGetLastError();
@@ -1038,4 +1093,43 @@ extern "C" int b200_moe_grouped_gemm(const void* X, const void* W, void* Y, int 
       return B200_ERR_INVALID;
   }
 #undef B200_GRP_CASE
+}
+
+// The same with the options of the other routed designs: gated != 0 applies gated_pair(act, limit) over interleaved
+// gate / up rows (Y [capacity_rows, N/2] bf16); otherwise Y is bf16 or, out_f32 != 0, fp32, times row_scale if given.
+// Tiles whose expert index is >= num_experts read weight rows beyond the stack (zeros): their output is not used.
+extern "C" int b200_moe_grouped_gemm_ex(const void* X, const void* W, void* Y, int capacity_rows, int N, int K,
+                                        int num_experts, int64_t ldx, int64_t ldw, int64_t ldy, const float* row_scale,
+                                        const int32_t* tile_expert, const int32_t* num_tiles, int block_x, int gated,
+                                        int act, float limit, int out_f32, void* stream) {
+  B200_REQUIRE(capacity_rows > 0 && N > 0 && K > 0 && num_experts >= 1, "moe_grouped_gemm: bad shape");
+  B200_REQUIRE(K % kBlockK == 0, "moe_grouped_gemm: K=%d must be a multiple of %d", K, kBlockK);
+  B200_REQUIRE(N % (2 * kBlockW) == 0, "moe_grouped_gemm: N=%d per expert must be a multiple of %d", N, 2 * kBlockW);
+  B200_REQUIRE(block_x > 0 && capacity_rows % block_x == 0, "moe_grouped_gemm: capacity_rows must be a multiple of block_x");
+  B200_REQUIRE(!gated || (row_scale == nullptr && !out_f32 && act >= 0 && act <= 2), "moe_grouped_gemm: gated output is bf16 without row_scale");
+  B200_REQUIRE(ldx >= K && ldw >= K && ldy >= (gated ? N / 2 : N), "moe_grouped_gemm: leading dimensions too small");
+  B200_REQUIRE(tile_expert && num_tiles, "moe_grouped_gemm: null tile tables");
+  const DeviceInfo& d = device_info();
+  if (!d.valid || d.cc_major != 10) {
+    b200_set_error("moe_grouped_gemm: tcgen05 kernel needs an sm_100 device (found cc %d.%d)", d.cc_major, d.cc_minor);
+    return B200_ERR_UNSUPPORTED;
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  const int fl = gated ? gated_flags(act, limit) : (out_f32 ? 1 : 0);
+#define B200_GRPX_CASE(BX)                                                                                        \
+  case BX:                                                                                                        \
+    return gated ? launch_gemm_grouped<BX, 1>(X, W, Y, capacity_rows, N, K, num_experts, ldx, ldw, ldy, nullptr,   \
+                                              tile_expert, num_tiles, s, fl)                                      \
+                 : launch_gemm_grouped<BX, 0>(X, W, Y, capacity_rows, N, K, num_experts, ldx, ldw, ldy, row_scale, \
+                                              tile_expert, num_tiles, s, fl);
+  switch (block_x) {
+    B200_GRPX_CASE(32)
+    B200_GRPX_CASE(64)
+    B200_GRPX_CASE(128)
+    B200_GRPX_CASE(256)
+    default:
+      b200_set_error("moe_grouped_gemm: block_x=%d unsupported (32,64,128,256)", block_x);
+      return B200_ERR_INVALID;
+  }
+#undef B200_GRPX_CASE
 }

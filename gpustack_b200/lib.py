@@ -99,6 +99,9 @@ SIGNATURES = {
     "b200_linear_simt_grouped": (_i32, [_vp, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _i64, _i64,
                                         _i64, _vp, _i32, _vp, _vp, _i32, _i64, _vp, _i32, _f32, _vp]),
     "b200_simt_group_rows": (_i32, []),
+    "b200_gemm_bf16_gated": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _f32, _vp]),
+    "b200_moe_grouped_gemm_ex": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _i32,
+                                        _i32, _f32, _i32, _vp]),
     "b200_moe_route_biased": (_i32, [_vp, _i64, _vp, _vp, _vp, _i32, _i32, _i32, _f32, _vp]),
     "b200_moe_combine_mixed": (_i32, [_vp, _i32, _i64, _vp, _vp, _vp, _vp, _i32, _i64, _vp, _i64, _vp, _i64, _i32, _i32,
                                       _i32, _i32, _vp]),

@@ -638,9 +638,20 @@ def linear_simt_grouped(x, w, out, M, N, K, ldx, ldw, ldy, batch=1, bsx=0, bsw=0
 
 
 def head_linear(x, w, out, H: int, n: int, k: int, x_head: int, out_head: int):
-    """Per-head linear: out[t, h*out_head : +n] = w[h] (n x k, contiguous) @ x[t, h*x_head : +k] for every head."""
+    """Per-head linear: out[t, h*out_head : +n] = w[h] (n x k, contiguous) @ x[t, h*x_head : +k] for every head.
+    bf16 with k a multiple of 64 and 16-byte aligned head slices: one tcgen05 GEMM per head over strided views;
+    otherwise ONE batched CUDA-core launch."""
+    if (x.dtype == torch.bfloat16 and H <= TC_HEAD_LINEAR_MAX_HEADS and _tc_gemm_ok(x, w, out, k) and x_head % 8 == 0 and (n * k) % 8 == 0
+            and (out_head * out.element_size()) % 16 == 0):
+        w3 = w.view(H, n, k)
+        for h in range(H):
+            gemm(x[:, h * x_head:h * x_head + k], w3[h], out=out[:, h * out_head:h * out_head + n], out_dtype=out.dtype)
+        return out
     return linear_simt_grouped(x, w, out, x.shape[0], n, k, x.stride(0), k, out.stride(0), batch=H, bsx=x_head, bsw=n * k,
                                bsy=out_head)
+
+
+TC_HEAD_LINEAR_MAX_HEADS = 128
 
 
 def _tc_gemm_ok(x, w, out, K) -> bool:
@@ -649,11 +660,27 @@ def _tc_gemm_ok(x, w, out, K) -> bool:
             and out.data_ptr() % 16 == 0)
 
 
+TC_GATED_ACTS = {"gelu_tanh": 1, "clamped_swish": 2}
+
+
 def gated_linear(x, w_interleaved, out, act: str, limit: float = 0.0):
     """out = act(x @ gate.T) (*) (x @ up.T) with interleaved gate / up rows (weights._interleave_rows); the
-    activation is computed in fp32 from the fp32 accumulators and rounded once."""
+    activation is computed in fp32 from the fp32 accumulators and rounded once.  bf16 in and out with K a multiple
+    of 64: the tcgen05 GEMM with the activation in its epilogue; otherwise the CUDA-core kernel."""
     M, K = x.shape
     N = w_interleaved.shape[0] // 2
+    if out.dtype == torch.bfloat16 and act in TC_GATED_ACTS and _tc_gemm_ok(x, w_interleaved, out, K):
+        timed = TIMER is not None and not torch.cuda.is_current_stream_capturing()
+        if timed:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        check(load().b200_gemm_bf16_gated(_p(x), _p(w_interleaved), _p(out), M, 2 * N, K, x.stride(0), w_interleaved.stride(0),
+                                          out.stride(0), TC_GATED_ACTS[act], limit, _stream()), "gemm_gated")
+        if timed:
+            e1.record()
+            TIMER.records.append(("gemm_prefill" if M > 256 else "gemm_decode", 4.0 * M * N * K,
+                                  2.0 * (2 * N * K + M * K) + 2.0 * M * N, e0, e1))
+        return out
     return linear_simt_grouped(x, w_interleaved, out, M, N, K, x.stride(0), w_interleaved.stride(0), out.stride(0),
                                act=GATED_ACTS[act], limit=limit)
 
@@ -672,7 +699,8 @@ class RoutedWorkspace:
     def __init__(self, max_tokens: int, top_k: int, e_total: int, D: int, ff: int, act_dtype, device):
         self.bx = simt_group_rows()
         n_pairs = max_tokens * top_k
-        self.capacity = moe_capacity_rows(n_pairs, e_total, self.bx)
+        self.capacity = max(moe_capacity_rows(n_pairs, e_total, bx) for bx in (32, 64, 128, 256))
+        self.xp = None            # gathered input rows of the tensor-core path, allocated at its first use
         i32 = lambda *s: torch.empty(*s, dtype=torch.int32, device=device)   # noqa: E731
         self.logits = torch.empty(max_tokens, e_total, dtype=torch.float32, device=device)
         self.topk_ids, self.topk_w = i32(n_pairs), torch.empty(n_pairs, dtype=torch.float32, device=device)
@@ -695,17 +723,30 @@ def routed_experts(x, router, correction, w13, w2, ws: RoutedWorkspace, out, n_r
     T, D = x.shape
     E = n_real + n_identity
     n_pairs = T * top_k
-    cap = moe_capacity_rows(n_pairs, E, ws.bx)
+    # tensor cores when both expert products fit the grouped tcgen05 GEMM (bf16, K multiples of 64, 256-row weight pairs)
+    tc = (x.dtype == torch.bfloat16 and n_real > 0 and D % 256 == 0 and ff % 128 == 0 and x.is_contiguous()
+          and w13.stride(0) == D and w2.stride(0) == ff)
+    bx = moe_block_x(n_pairs, E) if tc else ws.bx
+    cap = moe_capacity_rows(n_pairs, E, bx)
     if cap > ws.capacity:
         raise B200Error(f"routed_experts: {T} tokens exceed the workspace ({ws.capacity} rows)")
     L, st = load(), _stream()
     lg = ws.logits[:T]
     linear(x, router, lg)                                           # fp32 logits
     moe_route_biased(lg, correction, top_k, scale, ws.topk_ids, ws.topk_w, E)
-    check(L.b200_moe_align(_p(ws.topk_ids), _p(ws.topk_w), n_pairs, E, ws.bx, cap, _p(ws.pair_row), _p(ws.row_pair),
+    check(L.b200_moe_align(_p(ws.topk_ids), _p(ws.topk_w), n_pairs, E, bx, cap, _p(ws.pair_row), _p(ws.row_pair),
                            _p(ws.row_weight), _p(ws.tile_expert), _p(ws.num_tiles), st), "moe_align")
     act = ws.act[:cap * ff].view(cap, ff)
-    if n_real:
+    if tc:
+        if ws.xp is None:
+            ws.xp = torch.empty(ws.capacity, D, dtype=torch.bfloat16, device=x.device)
+        check(L.b200_moe_gather(_p(x), _p(ws.row_pair), _p(ws.num_tiles), _p(ws.xp), D, top_k, cap, st), "moe_gather")
+        check(L.b200_moe_grouped_gemm_ex(_p(ws.xp), _p(w13), _p(act), cap, 2 * ff, D, n_real, D, D, ff, None,
+                                         _p(ws.tile_expert), _p(ws.num_tiles), bx, 1, TC_GATED_ACTS["clamped_swish"], limit, 0,
+                                         st), "moe_grouped_gemm(gate_up)")
+        check(L.b200_moe_grouped_gemm_ex(_p(act), _p(w2), _p(ws.yp), cap, D, ff, n_real, ff, ff, D, _p(ws.row_weight),
+                                         _p(ws.tile_expert), _p(ws.num_tiles), bx, 0, 0, 0.0, 1, st), "moe_grouped_gemm(down)")
+    elif n_real:
         linear_simt_grouped(x, w13, act, cap, ff, D, x.stride(0), w13.stride(0), ff, row_pair=ws.row_pair, top_k=top_k,
                             tile_expert=ws.tile_expert, num_tiles=ws.num_tiles, n_real=n_real, w_expert=2 * ff * w13.stride(0),
                             act=GATED_ACTS["clamped_swish"], limit=limit)

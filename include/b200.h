@@ -341,6 +341,15 @@ int b200_linear_simt_grouped(const void* X, int x_f32, const void* W, void* Y, i
                              const int32_t* row_pair, int top_k, const int32_t* tile_expert, const int32_t* num_tiles,
                              int n_real, int64_t w_expert, const float* row_scale, int act, float limit, void* stream);
 int b200_simt_group_rows(void);
+/* The tcgen05 GEMM with a gated epilogue over interleaved gate / up rows (bf16 Y [M, N/2], K % 64 == 0):
+ * act 0 silu(g) u (factors rounded to bf16), 1 gelu_tanh(g) u, 2 clamped g sigmoid(1.702 g) (u + 1). */
+int b200_gemm_bf16_gated(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx, int64_t ldw,
+                         int64_t ldy, int act, float limit, void* stream);
+/* b200_moe_grouped_gemm with those activations (gated != 0) or an fp32 output (out_f32 != 0, with row_scale). */
+int b200_moe_grouped_gemm_ex(const void* X, const void* W, void* Y, int capacity_rows, int N, int K, int num_experts,
+                             int64_t ldx, int64_t ldw, int64_t ldy, const float* row_scale, const int32_t* tile_expert,
+                             const int32_t* num_tiles, int block_x, int gated, int act, float limit, int out_f32,
+                             void* stream);
 /* Softmax over E fp32 router outputs, top K of score + correction, weights score / (sum + 1e-20) * scale. */
 int b200_moe_route_biased(const float* logits, int64_t ld, const float* correction, int32_t* topk_ids, float* topk_w,
                           int T, int E, int K, float scale, void* stream);

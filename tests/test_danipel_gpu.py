@@ -301,6 +301,49 @@ def test_routed_experts_with_identity_and_shared_expert(dtype, E, ident, top, ff
     assert _rel(out, want) < (5e-6 if dtype == torch.float32 else 2e-2)
 
 
+def test_tensor_core_routes_of_the_per_head_gated_and_routed_products():
+    """bf16 shapes that the tcgen05 GEMMs take (K multiples of 64, 16-byte aligned slices): per-head products over strided
+    views, the gated epilogues, the grouped expert GEMMs with an fp32 weighted output; 300 rows = several tiles."""
+    from gpustack_b200 import ops
+    from gpustack_b200.weights import _interleave_rows
+
+    g = torch.Generator().manual_seed(9)
+    T, H, n, k = 300, 3, 40, 64
+    x = torch.randn(T, H * (k + 8), generator=g).to(BF)
+    w = (torch.randn(H, n, k, generator=g) / math.sqrt(k)).to(BF)
+    out = torch.zeros(T, H * (n + 8), device="cuda", dtype=BF)
+    ops.head_linear(x.cuda(), w.cuda(), out, H, n=n, k=k, x_head=k + 8, out_head=n + 8)
+    want = torch.einsum("thk,hnk->thn", x.view(T, H, k + 8)[..., :k].to(F64), w.to(F64))
+    assert _rel(out.view(T, H, n + 8)[..., :n].float(), want) < 1e-2
+    assert bool((out.view(T, H, n + 8)[..., n:] == 0).all())                 # the gaps between the heads' outputs stay untouched
+    K, N = 128, 192
+    xx = torch.randn(T, K, generator=g).to(BF)
+    gate, up = [(2.0 * torch.randn(N, K, generator=g) / math.sqrt(K)).to(BF) for _ in range(2)]
+    for act, lim, ref in (("gelu_tanh", 0.0, lambda a, b: O.gelu_tanh(a) * b),
+                          ("clamped_swish", 0.7, lambda a, b: (lambda gg, uu: gg * torch.sigmoid(1.702 * gg) * (uu + 1))(a.clamp(max=0.7), b.clamp(-0.7, 0.7)))):
+        o = torch.empty(T, N, device="cuda", dtype=BF)
+        ops.gated_linear(xx.cuda(), _interleave_rows(gate, up).cuda(), o, act, lim)
+        assert _rel(o.float(), ref(xx.to(F64) @ gate.to(F64).T, xx.to(F64) @ up.to(F64).T)) < 1e-2, act
+    E, ident, top, ff, D = 4, 1, 2, 128, 256
+    spec = _moe(E, ident, top, ff, 1.2, 1.7)
+    wm = {"router": 3 * torch.randn(E + ident, D, generator=g) / math.sqrt(D), "correction": 0.1 * torch.randn(E + ident, generator=g)}
+    for e in range(E):
+        wm[f"e{e}.gate"], wm[f"e{e}.up"] = [2 * torch.randn(ff, D, generator=g) / math.sqrt(D) for _ in range(2)]
+        wm[f"e{e}.down"] = torch.randn(D, ff, generator=g) / math.sqrt(ff)
+    wm = {k_: v.to(BF) for k_, v in wm.items()}
+    xm = torch.randn(T, D, generator=g).to(BF)
+    want = O.moe_mlp(xm.to(F64), {k_: v.to(F64) for k_, v in wm.items()}, spec)
+    ws = ops.RoutedWorkspace(320, top, E + ident, D, ff, BF, "cuda")
+    w13 = torch.cat([_interleave_rows(wm[f"e{e}.gate"], wm[f"e{e}.up"]) for e in range(E)]).cuda()
+    w2 = torch.cat([wm[f"e{e}.down"] for e in range(E)]).cuda()
+    outm = torch.empty(T, D, device="cuda")
+    for rows in (T, 3):                                                      # prompt-sized and decode-sized steps
+        ops.routed_experts(xm[:rows].cuda().contiguous(), wm["router"].cuda(), wm["correction"].float().cuda(), w13, w2, ws, outm[:rows], E, ident, top,
+                           1.7, ff, 1.2)
+        assert ws.xp is not None                                            # the tensor-core path ran
+        assert _rel(outm[:rows], want[:rows]) < 2e-2
+
+
 def _latent_case(dtype, n_keys, page, H, R, dr, seed, perm=True):
     """Cache rows for one sequence of n_keys tokens in shuffled pages, junk in the pages it does not own."""
     g = torch.Generator().manual_seed(seed)
