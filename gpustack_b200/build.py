@@ -32,6 +32,7 @@ SOURCES = [
     "mlstm.cu",
     "streams.cu",
     "latent.cu",
+    "latent_attention_mma.cu",
     "gemm_simt_grouped.cu",
     "moe_biased.cu",
 ]
@@ -57,6 +58,7 @@ STREAMS_LATENT_SOURCES = [
     "gemm_simt_grouped.cu",
     "streams.cu",
     "latent.cu",
+    "latent_attention_mma.cu",
     "attention_sink.cu",
 ]
 ROUTED_SOURCES = ["moe.cu", "moe_biased.cu"]

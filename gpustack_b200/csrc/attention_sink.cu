@@ -27,7 +27,7 @@ __device__ __forceinline__ float as_f32(bf16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ void as_store(float* p, float v) { *p = v; }
 __device__ __forceinline__ void as_store(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-constexpr int kMaxDvPerLane = 8;   // value width <= 256
+constexpr int kMaxDvLanes = 16;    // value width <= 512: kernels are built for 8 (<= 256) and 16 columns per lane
 
 // ----------------------------------------------------------------------------------------- prep
 // One warp per (token, head slot): slots [0, H) are query heads, [H, H + G) key heads, [H + G, H + 2G) value
@@ -183,7 +183,7 @@ constexpr int kPfRows = 16, kPfKeys = 32, kPfWarps = 4, kPfRowsPerWarp = kPfRows
 // grid (tiles, H, tile_rows / 16).  Tile i = rows [tile_q0[i], +tile_rows) of sequence tile_seq[i], cut into
 // 16-row pieces along z; the sequence's new rows are [cu_q[s], cu_q[s+1]) of the projection and sit at
 // positions ctx_lens[s] + row.
-template <typename TA>
+template <typename TA, int kMaxDvPerLane>
 __global__ void __launch_bounds__(kPfWarps * 32)
 attn_sink_prefill_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, const TA* __restrict__ k_cache,
                          const TA* __restrict__ v_cache, const int32_t* __restrict__ block_table, int max_blocks,
@@ -310,7 +310,7 @@ constexpr int kDecWarps = 4;
 // take 32-key blocks in turn.  Scores: lane = key, the (scaled) query is broadcast from shared memory and every
 // lane walks its own key row (16-byte loads when VEC); one max / sum reduction per 32 keys.  Values: lane = column,
 // the 32 probabilities and page offsets go round by shuffle, value rows are read contiguously.
-template <typename TA, bool VEC>
+template <typename TA, bool VEC, int kMaxDvPerLane>
 __global__ void __launch_bounds__(kDecWarps * 32)
 attn_sink_decode_kernel(const TA* __restrict__ proj, int64_t ld, int gate_col, const TA* __restrict__ k_cache,
                         const TA* __restrict__ v_cache, const int32_t* __restrict__ block_table, int max_blocks,
@@ -463,7 +463,7 @@ extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int
   B200_REQUIRE(v_ld >= dv, "attn_sink_prefill: value row pitch %lld < dv=%d", (long long)v_ld, dv);
   B200_REQUIRE(tile_rows > 0 && tile_rows % kPfRows == 0, "attn_sink_prefill: tiles of %d rows (multiples of %d)",
                tile_rows, kPfRows);
-  B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 32 * kMaxDvPerLane && page > 0,
+  B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 32 * kMaxDvLanes && page > 0,
                "attn_sink_prefill: bad shape H=%d G=%d dk=%d dv=%d", H, G, dk, dv);
   if (n_tiles <= 0) return B200_OK;
   const size_t smem = sizeof(float) * ((size_t)kPfRows * dk + (size_t)kPfKeys * (dk + 1) + (size_t)kPfKeys * dv +
@@ -471,19 +471,18 @@ extern "C" int b200_attn_sink_prefill(const void* proj, int f32, int64_t ld, int
   B200_REQUIRE(smem <= 200 * 1024, "attn_sink_prefill: head widths %d / %d exceed shared memory", dk, dv);
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(n_tiles, H, tile_rows / kPfRows);
-  if (f32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(attn_sink_prefill_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attn_sink_prefill_kernel<float><<<grid, kPfWarps * 32, smem, s>>>(
-        (const float*)proj, ld, gate_col, (const float*)k_cache, (const float*)v_cache, block_table, max_blocks, cu_q,
-        ctx_lens, tile_seq, tile_q0, sink, (float*)out, ldo, H, G, dk, dv, page, scale, v_ld);
-  } else {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(attn_sink_prefill_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attn_sink_prefill_kernel<bf16><<<grid, kPfWarps * 32, smem, s>>>(
-        (const bf16*)proj, ld, gate_col, (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_blocks, cu_q,
-        ctx_lens, tile_seq, tile_q0, sink, (bf16*)out, ldo, H, G, dk, dv, page, scale, v_ld);
-  }
+#define B200_PF(TA, L)                                                                                             \
+  do {                                                                                                             \
+    if (smem > 48 * 1024)                                                                                          \
+      cudaFuncSetAttribute(attn_sink_prefill_kernel<TA, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    attn_sink_prefill_kernel<TA, L><<<grid, kPfWarps * 32, smem, s>>>(                                             \
+        (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, cu_q,       \
+        ctx_lens, tile_seq, tile_q0, sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld);                        \
+  } while (0)
+  const bool wide = dv > 256;
+  if (f32) { if (wide) B200_PF(float, 16); else B200_PF(float, 8); }
+  else { if (wide) B200_PF(bf16, 16); else B200_PF(bf16, 8); }
+#undef B200_PF
   return b200_check_launch("b200_attn_sink_prefill");
 }
 
@@ -493,7 +492,7 @@ extern "C" int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int 
                                      int G, int dk, int dv, int page, float scale, int64_t v_ld, void* stream) {
   if (v_ld <= 0) v_ld = dv;
   B200_REQUIRE(v_ld >= dv, "attn_sink_decode: value row pitch %lld < dv=%d", (long long)v_ld, dv);
-  B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 32 * kMaxDvPerLane && page > 0,
+  B200_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && dv <= 32 * kMaxDvLanes && page > 0,
                "attn_sink_decode: bad shape H=%d G=%d dk=%d dv=%d", H, G, dk, dv);
   if (B <= 0) return B200_OK;
   cudaStream_t s = (cudaStream_t)stream;
@@ -503,7 +502,12 @@ extern "C" int b200_attn_sink_decode(const void* proj, int f32, int64_t ld, int 
   const bool vec = (dk * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0;
   dim3 grid(B, H);
 #define B200_DEC(TA, V)                                                                                          \
-  attn_sink_decode_kernel<TA, V><<<grid, kDecWarps * 32, smem, s>>>(                                             \
+  if (dv > 256)                                                                                                  \
+    attn_sink_decode_kernel<TA, V, 16><<<grid, kDecWarps * 32, smem, s>>>(                                       \
+        (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, seq_lens, \
+        sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld);                                                   \
+  else                                                                                                           \
+    attn_sink_decode_kernel<TA, V, 8><<<grid, kDecWarps * 32, smem, s>>>(                                        \
       (const TA*)proj, ld, gate_col, (const TA*)k_cache, (const TA*)v_cache, block_table, max_blocks, seq_lens,   \
       sink, (TA*)out, ldo, H, G, dk, dv, page, scale, v_ld)
   if (f32) { if (vec) B200_DEC(float, true); else B200_DEC(float, false); }

@@ -1,0 +1,340 @@
+// Latent attention in the absorbed form on the tensor cores (bf16): every head of a query row scores against
+// the SAME cached row per token,  [latent: R | rotated key part: dr]  (W = R + dr wide), and takes the first R
+// entries of those rows as its values.  So the heads are the M rows of the matrix products: a CTA owns 16
+// (query row, head) pairs -- 16 heads of one row, or 16 / HB rows of HB heads when the model has fewer heads --
+// and streams the sequence's cache rows ONCE for all of them, 64 keys at a time through a double-buffered
+// cp.async pipeline (key rows land in shared memory with a 16-byte pad per row, conflict-free for ldmatrix).
+//
+// Per 64-key block, with 4 warps:
+//   S:   warp w scores the 16 pairs against keys [16 w, 16 w + 16)          (mma.sync m16n8k16, k over W)
+//   max: the block's row maxima are exchanged through shared memory; every warp keeps the same running
+//        maximum m and rescales its accumulators by 2^(m_old - m_new)       (fp32, base-2 domain)
+//   P:   exp2(S - m) is written to shared memory as bf16 [16][64]; each warp keeps the fp32 sum of its own
+//        16 columns (the four partial sums meet at the end)
+//   O:   warp w accumulates O[16][R/4 columns from w R/4] += P V, V = the block's rows read transposed.
+// The end: l = sum of the partial sums (+ exp(sink_h - m): a learned per-head term of the denominator with no key
+// and no value), O / l, one rounding to bf16.  Causal: pair (row i, head) sees keys 0 .. p0 + i.
+// One kernel serves prompt portions (tile list, as the other prefill kernels) and single new rows (decode).
+// Shapes: W a multiple of 16, R a multiple of 64 up to 512; anything else runs on the generic kernels.
+#include "common.cuh"
+#include "runtime.h"
+#include "../../include/b200.h"
+
+#include <math.h>
+
+namespace b200 {
+
+constexpr int kLaWarps = 4, kLaKeys = 64, kLaRows = 16;
+constexpr int kLaPPitch = kLaKeys * 2 + 16;          // bytes per row of the probability tile
+
+struct LaArgs {
+  const bf16* qa;
+  int64_t ldq;
+  const bf16* cache;
+  int page;
+  const int32_t* block_table;
+  int max_blocks;
+  const int32_t* cu_q;        // prompt portions: tile list (tile_seq != NULL)
+  const int32_t* ctx_lens;
+  const int32_t* tile_seq;
+  const int32_t* tile_q0;
+  const int32_t* seq_lens;    // single rows: row b sees keys [0, seq_lens[b])
+  const float* sink;
+  bf16* out;
+  int64_t ldo;
+  int H, W, R, HB;            // HB heads per CTA (a power of two <= 16), 16 / HB query rows per CTA
+  float scale_log2;
+};
+
+template <int NT>   // n-tiles (8 columns) of the output per warp: R = 32 NT
+__global__ void __launch_bounds__(kLaWarps * 32)
+latent_attn_mma_kernel(LaArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int W = a.W, R = a.R, HB = a.HB, QR = kLaRows / HB;
+  const int pitch = W * 2 + 16;                       // bytes; W / 8 chunks + 1: odd, so 8 rows hit 8 bank groups
+  uint8_t* q_s = smem;
+  uint8_t* k_s = q_s + kLaRows * pitch;               // [2][64][pitch]
+  uint8_t* p_s = k_s + 2 * kLaKeys * pitch;           // [16][kLaPPitch]
+  float* red_m = reinterpret_cast<float*>(p_s + kLaRows * kLaPPitch);   // [4][16]
+  float* red_l = red_m + kLaWarps * kLaRows;                            // [4][16]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h0 = blockIdx.y * HB;
+
+  int s, nq, p0;
+  size_t grow0;
+  if (a.tile_seq != nullptr) {
+    s = a.tile_seq[blockIdx.x];
+    const int q0 = a.tile_q0[blockIdx.x] + QR * blockIdx.z;
+    const int row0 = a.cu_q[s], qlen = a.cu_q[s + 1] - row0;
+    if (q0 >= qlen) return;
+    nq = min(QR, qlen - q0);
+    p0 = a.ctx_lens[s] + q0;
+    grow0 = (size_t)(row0 + q0);
+  } else {
+    s = blockIdx.x;
+    nq = 1;
+    p0 = a.seq_lens[s] - 1;
+    grow0 = (size_t)s;
+    if (p0 < 0) {                                      // a padding row of a captured batch: defined output, no keys
+      for (int i = threadIdx.x; i < HB * R; i += blockDim.x) {
+        const int h = h0 + i / R;
+        if (h < a.H) a.out[grow0 * a.ldo + (size_t)h * R + i % R] = __float2bfloat16_rn(0.f);
+      }
+      return;
+    }
+  }
+  const int kv_end = p0 + nq;
+  const int n_blk = (kv_end + kLaKeys - 1) / kLaKeys;
+  const int32_t* bt = a.block_table + (size_t)s * a.max_blocks;
+  const int cpr = W / 8;                               // 16-byte chunks per row
+
+  auto issue = [&](int blk) {
+    uint8_t* dst = k_s + (blk & 1) * kLaKeys * pitch;
+    const int k0 = blk * kLaKeys;
+    for (int ci = threadIdx.x; ci < kLaKeys * cpr; ci += blockDim.x) {
+      const int r = ci / cpr, c = ci - r * cpr;
+      const int key = k0 + r;
+      const bool live = key < kv_end;
+      const int kk = live ? key : 0;
+      const bf16* src = a.cache + ((size_t)bt[kk / a.page] * a.page + (kk % a.page)) * W + c * 8;
+      cp_async_16_zfill(dst + r * pitch + c * 16, src, live);
+    }
+  };
+  issue(0);
+  cp_async_commit();
+
+  // ---- the 16 (row, head) pairs' absorbed queries
+  for (int ci = threadIdx.x; ci < kLaRows * cpr; ci += blockDim.x) {
+    const int i = ci / cpr, c = ci - i * cpr;
+    const int qi = i / HB, h = h0 + i % HB;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (qi < nq && h < a.H) v = ld_v4(a.qa + (grow0 + qi) * a.ldq + (size_t)h * W + c * 8);
+    *reinterpret_cast<uint4*>(q_s + i * pitch + c * 16) = v;
+  }
+
+  float o[NT][4];
+#pragma unroll
+  for (int t = 0; t < NT; ++t) o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  const int r0 = lane >> 2, r1 = r0 + 8;
+  const int lim0 = p0 + r0 / HB, lim1 = p0 + r1 / HB;   // last visible key of this lane's two rows
+  const uint32_t q_base = smem_u32(q_s), p_base = smem_u32(p_s);
+  const int ai = lane >> 3, arr = lane & 7;
+  const int a_row = arr + (ai & 1) * 8;                 // A-operand (row-major 16 x 16) ldmatrix addressing
+  const int b_tok = arr + (ai >> 1) * 8;                // B-operand of S: keys as n
+  const int v_tok = arr + (ai & 1) * 8;                 // B-operand of P V: keys as k (transposed load)
+  const int ks_n = W / 16;
+  const int col_chunk0 = warp * (R / 4) / 8;            // first 16-byte chunk of this warp's output columns
+
+  for (int blk = 0; blk < n_blk; ++blk) {
+    if (blk + 1 < n_blk) issue(blk + 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();                                    // block blk (and, first time, the queries) visible to all
+    const uint32_t k_base = smem_u32(k_s + (blk & 1) * kLaKeys * pitch);
+
+    // S: 16 pairs x this warp's 16 keys
+    float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    {
+      const uint32_t qa_addr = q_base + a_row * pitch + (ai >> 1) * 16;
+      const uint32_t kb_addr = k_base + (warp * 16 + b_tok) * pitch + (ai & 1) * 16;
+      for (int ks = 0; ks < ks_n; ++ks) {
+        uint32_t qf[4], b0, b1, b2, b3;
+        ldsm_x4(qa_addr + ks * 32, qf[0], qf[1], qf[2], qf[3]);
+        ldsm_x4(kb_addr + ks * 32, b0, b1, b2, b3);
+        mma_bf16_16816(sc[0], qf, b0, b1);
+        mma_bf16_16816(sc[1], qf, b2, b3);
+      }
+    }
+    const int key0 = blk * kLaKeys + warp * 16 + 2 * (lane & 3);
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = key0 + t * 8 + (e & 1);
+        const bool seen = key <= (e < 2 ? lim0 : lim1);
+        const float v = seen ? sc[t][e] * a.scale_log2 : -INFINITY;
+        sc[t][e] = v;
+        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    if ((lane & 3) == 0) {
+      red_m[warp * kLaRows + r0] = mx0;
+      red_m[warp * kLaRows + r1] = mx1;
+    }
+    __syncthreads();
+    float mn0 = m0, mn1 = m1;
+#pragma unroll
+    for (int w = 0; w < kLaWarps; ++w) {
+      mn0 = fmaxf(mn0, red_m[w * kLaRows + r0]);
+      mn1 = fmaxf(mn1, red_m[w * kLaRows + r1]);
+    }
+    // key 0 is visible to every pair, so after the first block both maxima are finite
+    const float a0 = exp2f(m0 - mn0), a1 = exp2f(m1 - mn1);
+    m0 = mn0;
+    m1 = mn1;
+    float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      sc[t][0] = exp2f(sc[t][0] - mn0); sc[t][1] = exp2f(sc[t][1] - mn0);
+      sc[t][2] = exp2f(sc[t][2] - mn1); sc[t][3] = exp2f(sc[t][3] - mn1);
+      rs0 += sc[t][0] + sc[t][1];
+      rs1 += sc[t][2] + sc[t][3];
+      const uint32_t colb = (uint32_t)(warp * 16 + t * 8 + 2 * (lane & 3)) * 2u;
+      st_shared_u32(p_base + r0 * kLaPPitch + colb, pack_bf16(sc[t][0], sc[t][1]));
+      st_shared_u32(p_base + r1 * kLaPPitch + colb, pack_bf16(sc[t][2], sc[t][3]));
+    }
+    l0 = l0 * a0 + rs0;
+    l1 = l1 * a1 + rs1;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) { o[t][0] *= a0; o[t][1] *= a0; o[t][2] *= a1; o[t][3] *= a1; }
+    __syncthreads();                                    // the whole probability tile is written
+
+    // O[16][this warp's R/4 columns] += P (16 x 64) V (64 x R/4)
+#pragma unroll
+    for (int kk = 0; kk < kLaKeys / 16; ++kk) {
+      uint32_t pa[4];
+      ldsm_x4(p_base + a_row * kLaPPitch + (2 * kk + (ai >> 1)) * 16, pa[0], pa[1], pa[2], pa[3]);
+      const uint32_t v_addr = k_base + (kk * 16 + v_tok) * pitch + (col_chunk0 + (ai >> 1)) * 16;
+#pragma unroll
+      for (int c = 0; c < NT; c += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(v_addr + c * 16, b0, b1, b2, b3);
+        mma_bf16_16816(o[c], pa, b0, b1);
+        mma_bf16_16816(o[c + 1], pa, b2, b3);
+      }
+    }
+    __syncthreads();                                    // this key buffer and the probability tile are free again
+  }
+  cp_async_wait<0>();
+
+  // ---- partial sums of the four warps, the sink, the division
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if ((lane & 3) == 0) {
+    red_l[warp * kLaRows + r0] = l0;
+    red_l[warp * kLaRows + r1] = l1;
+  }
+  __syncthreads();
+  float den0 = 0.f, den1 = 0.f;
+#pragma unroll
+  for (int w = 0; w < kLaWarps; ++w) {
+    den0 += red_l[w * kLaRows + r0];
+    den1 += red_l[w * kLaRows + r1];
+  }
+  const int qi0 = r0 / HB, hh0 = h0 + r0 % HB, qi1 = r1 / HB, hh1 = h0 + r1 % HB;
+  const bool ok0 = qi0 < nq && hh0 < a.H, ok1 = qi1 < nq && hh1 < a.H;
+  if (a.sink != nullptr) {
+    if (ok0) den0 += exp2f(a.sink[hh0] * 1.4426950408889634f - m0);
+    if (ok1) den1 += exp2f(a.sink[hh1] * 1.4426950408889634f - m1);
+  }
+  const float inv0 = den0 > 0.f ? 1.f / den0 : 0.f, inv1 = den1 > 0.f ? 1.f / den1 : 0.f;
+  const int cb = warp * (R / 4) + 2 * (lane & 3);
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    if (ok0)
+      *reinterpret_cast<uint32_t*>(a.out + (grow0 + qi0) * a.ldo + (size_t)hh0 * R + cb + t * 8) =
+          pack_bf16(o[t][0] * inv0, o[t][1] * inv0);
+    if (ok1)
+      *reinterpret_cast<uint32_t*>(a.out + (grow0 + qi1) * a.ldo + (size_t)hh1 * R + cb + t * 8) =
+          pack_bf16(o[t][2] * inv1, o[t][3] * inv1);
+  }
+}
+
+static size_t la_smem_bytes(int W) {
+  const size_t pitch = (size_t)W * 2 + 16;
+  return kLaRows * pitch + 2 * kLaKeys * pitch + kLaRows * kLaPPitch + 2 * kLaWarps * kLaRows * sizeof(float);
+}
+
+static int la_heads_per_cta(int H) {
+  int hb = 1;
+  while (hb * 2 <= H && hb < 16) hb *= 2;
+  return hb;
+}
+
+template <int NT>
+static int la_launch(const LaArgs& a, dim3 grid, cudaStream_t s) {
+  const size_t smem = la_smem_bytes(a.W);
+  static size_t attr = 0;
+  if (smem > attr) {
+    cudaError_t e = cudaFuncSetAttribute(latent_attn_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      b200_set_error("latent_attn: cudaFuncSetAttribute(smem=%zu): %s", smem, cudaGetErrorString(e));
+      return B200_ERR_CUDA;
+    }
+    attr = smem;
+  }
+  latent_attn_mma_kernel<NT><<<grid, kLaWarps * 32, smem, s>>>(a);
+  return b200_check_launch("b200_latent_attn");
+}
+
+static int la_dispatch(const LaArgs& a, dim3 grid, cudaStream_t s) {
+  switch (a.R / 32) {
+    case 2: return la_launch<2>(a, grid, s);
+    case 4: return la_launch<4>(a, grid, s);
+    case 6: return la_launch<6>(a, grid, s);
+    case 8: return la_launch<8>(a, grid, s);
+    case 12: return la_launch<12>(a, grid, s);
+    case 16: return la_launch<16>(a, grid, s);
+    default:
+      b200_set_error("latent_attn: latent width %d is not covered (64, 128, 192, 256, 384, 512)", a.R);
+      return B200_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// 1 when the tensor-core kernel takes this shape (bf16 only; the caller checks the element type).
+extern "C" int b200_latent_attn_covers(int H, int R, int dr) {
+  const int W = R + dr;
+  if (H <= 0 || R <= 0 || dr < 0 || W % 16 != 0) return 0;
+  if (!(R == 64 || R == 128 || R == 192 || R == 256 || R == 384 || R == 512)) return 0;
+  return la_smem_bytes(W) <= 220 * 1024 ? 1 : 0;
+}
+
+static int la_check(const void* qa, int64_t ldq, const void* cache, int64_t ldo, int H, int R, int dr) {
+  B200_REQUIRE(b200_latent_attn_covers(H, R, dr), "latent_attn: shape H=%d R=%d dr=%d is not covered", H, R, dr);
+  B200_REQUIRE(ldq % 8 == 0 && (reinterpret_cast<uintptr_t>(qa) & 15) == 0 && (reinterpret_cast<uintptr_t>(cache) & 15) == 0 &&
+                   ldo % 2 == 0,
+               "latent_attn: 16-byte aligned query and cache rows required");
+  return B200_OK;
+}
+
+extern "C" int b200_latent_attn_prefill(const void* qa, int64_t ldq, const void* cache, int page,
+                                        const int32_t* block_table, int max_blocks, const int32_t* cu_q,
+                                        const int32_t* ctx_lens, const int32_t* tile_seq, const int32_t* tile_q0,
+                                        int n_tiles, int tile_rows, const float* sink, void* out, int64_t ldo, int H, int R,
+                                        int dr, float scale, void* stream) {
+  if (int rc = la_check(qa, ldq, cache, ldo, H, R, dr)) return rc;
+  B200_REQUIRE(tile_rows > 0 && tile_rows % kLaRows == 0 && page > 0, "latent_attn_prefill: tiles of %d rows (multiples of %d)",
+               tile_rows, kLaRows);
+  if (n_tiles <= 0) return B200_OK;
+  const int hb = la_heads_per_cta(H);
+  LaArgs a{(const bf16*)qa, ldq, (const bf16*)cache, page, block_table, max_blocks, cu_q, ctx_lens, tile_seq, tile_q0, nullptr,
+           sink, (bf16*)out, ldo, H, R + dr, R, hb, scale * 1.4426950408889634f};
+  dim3 grid(n_tiles, (H + hb - 1) / hb, tile_rows / (kLaRows / hb));
+  return la_dispatch(a, grid, (cudaStream_t)stream);
+}
+
+extern "C" int b200_latent_attn_decode(const void* qa, int64_t ldq, const void* cache, int page,
+                                       const int32_t* block_table, int max_blocks, const int32_t* seq_lens, int B,
+                                       const float* sink, void* out, int64_t ldo, int H, int R, int dr, float scale,
+                                       void* stream) {
+  if (int rc = la_check(qa, ldq, cache, ldo, H, R, dr)) return rc;
+  B200_REQUIRE(page > 0, "latent_attn_decode: bad page size");
+  if (B <= 0) return B200_OK;
+  const int hb = la_heads_per_cta(H);
+  LaArgs a{(const bf16*)qa, ldq, (const bf16*)cache, page, block_table, max_blocks, nullptr, nullptr, nullptr, nullptr, seq_lens,
+           sink, (bf16*)out, ldo, H, R + dr, R, hb, scale * 1.4426950408889634f};
+  dim3 grid(B, (H + hb - 1) / hb, 1);
+  return la_dispatch(a, grid, (cudaStream_t)stream);
+}

@@ -284,10 +284,10 @@ class LayerListRunner(ModelRunner):
                         m.rot.layout == "half", lw.rot_freq, lw.rot_mag, eps)
         ops.head_linear(q, lw.uk_t, qa, H, n=R, k=dn, x_head=dn + dr, out_head=W)
         if nt:
-            ops.attn_sink_prefill(qa[:Tp], -1, cache, cache, bt_p, cu_p, ctx_p, ts, tq, lw.sink, o_lat[:Tp], H, 1, W, R,
-                                  m.scale, tile_rows=self.prefill_tile, v_ld=W)
+            ops.latent_attn_prefill(qa[:Tp], cache, bt_p, cu_p, ctx_p, ts, tq, lw.sink, o_lat[:Tp], H, R, dr, m.scale,
+                                    tile_rows=self.prefill_tile)
         if Bd:
-            ops.attn_sink_decode(qa[Tp:T], -1, cache, cache, bt_d, lens_d, lw.sink, o_lat[Tp:T], H, 1, W, R, m.scale, v_ld=W)
+            ops.latent_attn_decode(qa[Tp:T], cache, bt_d, lens_d, lw.sink, o_lat[Tp:T], H, R, dr, m.scale)
         ops.head_linear(o_lat, lw.uv, out, H, n=dv, k=R, x_head=R, out_head=dv)
         self.stats["kernel_launches"] += 3 + (1 if nt else 0) + (1 if Bd else 0)
 

@@ -621,6 +621,37 @@ def latent_prep(proj, kv_col: int, q, kv_norm_w, positions, slots, cache, qa, H,
                                   rot_dims, 1 if half_layout else 0, _p(freq), mag, eps, _stream()), "latent_prep")
 
 
+def latent_attn_covers(H: int, R: int, dr: int) -> bool:
+    return bool(load().b200_latent_attn_covers(H, R, dr))
+
+
+def latent_attn_prefill(qa, cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out, H, R, dr, scale,
+                        tile_rows: int = 0):
+    """Causal latent attention of prompt portions in the absorbed form: qa [T, H*(R+dr)], cache [blocks, 1, page, R+dr]
+    (one row per token for all heads; its first R entries are the values), out [T, H*R].  bf16 shapes the tensor-core
+    kernel covers run there, everything else (fp32, odd widths) on the generic kernel with one shared key head."""
+    _cuda(qa, cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out)
+    if qa.dtype == torch.bfloat16 and latent_attn_covers(H, R, dr) and qa.stride(0) % 8 == 0 and qa.data_ptr() % 16 == 0:
+        check(load().b200_latent_attn_prefill(_p(qa), qa.stride(0), _p(cache), cache.shape[2], _p(block_table),
+                                              block_table.shape[1], _p(cu_q), _p(ctx_lens), _p(tile_seq), _p(tile_q0),
+                                              tile_seq.shape[0], tile_rows or attn_sink_prefill_tile(), _p(sink), _p(out),
+                                              out.stride(0), H, R, dr, scale, _stream()), "latent_attn_prefill")
+        return out
+    return attn_sink_prefill(qa, -1, cache, cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out, H, 1, R + dr, R,
+                             scale, tile_rows=tile_rows, v_ld=R + dr)
+
+
+def latent_attn_decode(qa, cache, block_table, seq_lens, sink, out, H, R, dr, scale):
+    """The same for one new row per sequence (row b sees keys [0, seq_lens[b]))."""
+    _cuda(qa, cache, block_table, seq_lens, sink, out)
+    if qa.dtype == torch.bfloat16 and latent_attn_covers(H, R, dr) and qa.stride(0) % 8 == 0 and qa.data_ptr() % 16 == 0:
+        check(load().b200_latent_attn_decode(_p(qa), qa.stride(0), _p(cache), cache.shape[2], _p(block_table),
+                                             block_table.shape[1], _p(seq_lens), seq_lens.shape[0], _p(sink), _p(out),
+                                             out.stride(0), H, R, dr, scale, _stream()), "latent_attn_decode")
+        return out
+    return attn_sink_decode(qa, -1, cache, cache, block_table, seq_lens, sink, out, H, 1, R + dr, R, scale, v_ld=R + dr)
+
+
 def simt_group_rows() -> int:
     return load().b200_simt_group_rows()
 

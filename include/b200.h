@@ -334,6 +334,17 @@ int b200_latent_prep(const void* proj, int f32, int64_t ld, int kv_col, const vo
                      const void* kv_norm_w, const int32_t* positions, const int32_t* slots, void* cache, void* qa,
                      int64_t ldqa, int T, int H, int dn, int dr, int R, int dims, int half_layout, const double* freq,
                      float mag, float eps, void* stream);
+/* Latent attention on the tensor cores (bf16; csrc/latent_attention_mma.cu): qa [rows][H][R + dr] absorbed queries,
+ * cache [blocks][page][R + dr], out [rows][H][R]; sink [H] fp32 or NULL.  covers(): W = R + dr a multiple of 16 and
+ * R in {64, 128, 192, 256, 384, 512}.  prefill: tile list as b200_attn_sink_prefill; decode: one row per sequence. */
+int b200_latent_attn_covers(int H, int R, int dr);
+int b200_latent_attn_prefill(const void* qa, int64_t ldq, const void* cache, int page, const int32_t* block_table,
+                             int max_blocks, const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
+                             const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
+                             int64_t ldo, int H, int R, int dr, float scale, void* stream);
+int b200_latent_attn_decode(const void* qa, int64_t ldq, const void* cache, int page, const int32_t* block_table,
+                            int max_blocks, const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo,
+                            int H, int R, int dr, float scale, void* stream);
 /* Batched / grouped / gated linear on the CUDA cores (see gemm_simt_grouped.cu).  act: 0 plain, 1 gelu_tanh(g) u,
  * 2 clamped g sigmoid(1.702 g) (u + 1) with `limit`, 3 silu(g) u; act != 0: W rows interleaved gate / up, N pairs. */
 int b200_linear_simt_grouped(const void* X, int x_f32, const void* W, void* Y, int y_f32, int M, int N, int K,

@@ -357,47 +357,52 @@ def _latent_case(dtype, n_keys, page, H, R, dr, seed, perm=True):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, BF])
-@pytest.mark.parametrize("H,R,dr,sink", [(3, 20, 6, True), (16, 128, 64, False), (1, 256, 8, True)])
+@pytest.mark.parametrize("H,R,dr,sink", [(3, 20, 6, True), (16, 128, 64, False), (1, 256, 8, True), (20, 512, 64, True),
+                                         (3, 64, 16, False), (8, 192, 32, True), (2, 384, 32, False)])
 def test_attention_over_the_latent_cache_prefill_and_decode(dtype, H, R, dr, sink):
     """Absorbed form: every head scores against the same cache rows and takes their first R entries as values.
-    A portion of 21 rows after 30 cached tokens, then single rows, against the expanded-per-head oracle."""
+    A portion of 37 rows after 130 cached tokens (three 64-key blocks, ten pages), then single rows, against the
+    expanded-per-head oracle.  bf16 shapes with R a multiple of 64 run on the tensor-core kernel, the rest on the
+    generic one."""
     from gpustack_b200 import ops
 
-    page, ctx, new = 16, 30, 21
+    page, ctx, new = 16, 130, 37
     n = ctx + new
     C, cache, order = _latent_case(dtype, n, page, H, R, dr, seed=H + R)
     g = torch.Generator().manual_seed(1)
     q = torch.randn(new, H, R + dr, generator=g).to(dtype)
     sk = (torch.randn(H, generator=g) * 1.5) if sink else None
-    scale = 0.3 / math.sqrt(R + dr) * 4
+    scale = 1.2 / math.sqrt(R + dr)
     k = C.to(F64).unsqueeze(1).expand(n, H, R + dr)
     want = O.causal_softmax_attention(q.to(F64), k, k[..., :R], scale, sink=None if sk is None else sk.to(F64), q_pos0=ctx)
-    bt = torch.zeros(1, 8, dtype=torch.int32)
+    bt = torch.zeros(1, 16, dtype=torch.int32)
     bt[0, :len(order)] = order
     tile = ops.attn_sink_prefill_tile()
     ts, tq = ops.build_prefill_tiles([new], tile, [ctx])
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")   # noqa: E731
     out = torch.zeros(new, H * R, device="cuda", dtype=dtype)
     qd = q.reshape(new, -1).cuda()
-    ops.attn_sink_prefill(qd, -1, cache, cache, bt.cuda(), i32([0, new]), i32([ctx]), i32(ts), i32(tq), None if sk is None else sk.cuda(),
-                          out, H, 1, R + dr, R, scale, v_ld=R + dr)
+    skd = None if sk is None else sk.cuda()
+    ops.latent_attn_prefill(qd, cache, bt.cuda(), i32([0, new]), i32([ctx]), i32(ts), i32(tq), skd, out, H, R, dr, scale)
     tol = 5e-6 if dtype == torch.float32 else 1.5e-2
     assert _rel(out.view(new, H, R).float(), want) < tol
-    for r in (0, 1, 17, new - 1):           # the same rows one at a time through the decode kernel
-        o1 = torch.zeros(1, H * R, device="cuda", dtype=dtype)
-        ops.attn_sink_decode(qd[r:r + 1], -1, cache, cache, bt.cuda(), i32([ctx + r + 1]), None if sk is None else sk.cuda(), o1, H, 1,
-                             R + dr, R, scale, v_ld=R + dr)
-        assert _rel(o1.view(H, R).float(), want[r]) < tol
+    rows = [0, 1, 17, new - 1]
+    o4 = torch.zeros(len(rows) + 1, H * R, device="cuda", dtype=dtype)          # the last row: a padding row without keys
+    bt4 = bt.repeat(len(rows) + 1, 1).cuda()
+    ops.latent_attn_decode(qd[rows + [0]].contiguous(), cache, bt4, i32([ctx + r + 1 for r in rows] + [0]), skd, o4, H, R, dr, scale)
+    assert _rel(o4[:len(rows)].view(len(rows), H, R).float(), want[rows]) < tol
+    assert bool(torch.isfinite(o4[-1].float()).all())
 
 
 @pytest.mark.parametrize("kernel", ["prefill", "decode"])
-@pytest.mark.parametrize("far", [0, 15, 16, 17, 250])
-def test_one_far_key_stands_out_and_the_next_token_stays_invisible(kernel, far):
-    """400 cached tokens; the key at `far` (first token, page borders, far back) is made to dominate every head's
-    scores, so the output must be its latent.  A still larger key one place AFTER the query must not be seen."""
+@pytest.mark.parametrize("far", [0, 15, 16, 17, 63, 64, 250])
+@pytest.mark.parametrize("dtype,H,R,dr", [(torch.float32, 4, 24, 8), (BF, 4, 64, 16), (BF, 16, 128, 32)])
+def test_one_far_key_stands_out_and_the_next_token_stays_invisible(kernel, far, dtype, H, R, dr):
+    """400 cached tokens; the key at `far` (first token, page and key-block borders, far back) is made to dominate every
+    head's scores, so the output must be its latent.  A still larger key one place AFTER the query must not be seen."""
     from gpustack_b200 import ops
 
-    H, R, dr, page, n = 4, 24, 8, 16, 400
+    page, n = 16, 400
     g = torch.Generator().manual_seed(far)
     C = torch.randn(n + 1, R + dr, generator=g) * 0.1
     q = torch.randn(1, H, R + dr, generator=g) * 0.1
@@ -406,21 +411,22 @@ def test_one_far_key_stands_out_and_the_next_token_stays_invisible(kernel, far):
     C[far] += 40 * direction
     C[n] += 90 * direction                       # position n: the future for a query at n - 1
     q = q + direction
+    C, q = C.to(dtype), q.to(dtype)
     nb = (n + 1 + page - 1) // page
-    cache = torch.zeros(nb, 1, page, R + dr)
+    cache = torch.zeros(nb, 1, page, R + dr, dtype=dtype)
     cache.view(-1, R + dr)[:n + 1] = C
+    cache = cache.cuda()
     bt = torch.arange(nb, dtype=torch.int32).view(1, -1).cuda()
-    out = torch.zeros(1, H * R, device="cuda")
+    out = torch.zeros(1, H * R, device="cuda", dtype=dtype)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")   # noqa: E731
     sink = torch.zeros(H, device="cuda")
     if kernel == "prefill":
         ts, tq = ops.build_prefill_tiles([1], ops.attn_sink_prefill_tile(), [n - 1])
-        ops.attn_sink_prefill(q.reshape(1, -1).cuda(), -1, cache.cuda(), cache.cuda(), bt, i32([0, 1]), i32([n - 1]), i32(ts), i32(tq), sink,
-                              out, H, 1, R + dr, R, 1.0, v_ld=R + dr)
+        ops.latent_attn_prefill(q.reshape(1, -1).cuda(), cache, bt, i32([0, 1]), i32([n - 1]), i32(ts), i32(tq), sink, out, H, R, dr, 1.0)
     else:
-        ops.attn_sink_decode(q.reshape(1, -1).cuda(), -1, cache.cuda(), cache.cuda(), bt, i32([n]), sink, out, H, 1, R + dr, R, 1.0, v_ld=R + dr)
+        ops.latent_attn_decode(q.reshape(1, -1).cuda(), cache, bt, i32([n]), sink, out, H, R, dr, 1.0)
     for h in range(H):
-        assert torch.allclose(out.view(H, R)[h].cpu(), C[far, :R], atol=1e-4), (kernel, far, h)
+        assert torch.allclose(out.view(H, R)[h].float().cpu(), C[far, :R].float(), atol=1e-4 if dtype == torch.float32 else 2e-3), (kernel, far, h)
 
 
 # ------------------------------------------------------------------------------------ whole models
