@@ -2,8 +2,9 @@
 // the SAME cached row per token,  [latent: R | rotated key part: dr]  (W = R + dr wide), and takes the first R
 // entries of those rows as its values.  So the heads are the M rows of the matrix products: a CTA owns 16
 // (query row, head) pairs -- 16 heads of one row, or 16 / HB rows of HB heads when the model has fewer heads --
-// and streams the sequence's cache rows ONCE for all of them, 64 keys at a time through a double-buffered
-// cp.async pipeline (key rows land in shared memory with a 16-byte pad per row, conflict-free for ldmatrix).
+// and streams the sequence's cache rows ONCE for all of them, 64 keys at a time with cp.async (double-buffered while
+// two CTAs still fit an SM; with wide rows one buffer per CTA, and the two resident CTAs overlap each other's
+// fetches).  Key rows land in shared memory with a 16-byte pad per row, conflict-free for ldmatrix.
 //
 // Per 64-key block, with 4 warps:
 //   S:   warp w scores the 16 pairs against keys [16 w, 16 w + 16)          (mma.sync m16n8k16, k over W)
@@ -44,6 +45,11 @@ struct LaArgs {
   int64_t ldo;
   int H, W, R, HB;            // HB heads per CTA (a power of two <= 16), 16 / HB query rows per CTA
   float scale_log2;
+  int page_shift;             // log2(page)
+  int nsplit;                 // single rows only: the keys are cut into nsplit ranges (grid.z), partial results
+  float* ws;                  //   [row][head][split][R + 2] = unnormalised O, running maximum, partial sum -> merge kernel
+  int nbuf;                   // key buffers: 2 = the next block is fetched while this one is used; 1 (wide rows) = one
+                              // buffer, two CTAs per SM overlap each other's fetches instead
 };
 
 template <int NT>   // n-tiles (8 columns) of the output per warp: R = 32 NT
@@ -54,7 +60,7 @@ latent_attn_mma_kernel(LaArgs a) {
   const int pitch = W * 2 + 16;                       // bytes; W / 8 chunks + 1: odd, so 8 rows hit 8 bank groups
   uint8_t* q_s = smem;
   uint8_t* k_s = q_s + kLaRows * pitch;               // [2][64][pitch]
-  uint8_t* p_s = k_s + 2 * kLaKeys * pitch;           // [16][kLaPPitch]
+  uint8_t* p_s = k_s + a.nbuf * kLaKeys * pitch;      // [16][kLaPPitch]
   float* red_m = reinterpret_cast<float*>(p_s + kLaRows * kLaPPitch);   // [4][16]
   float* red_l = red_m + kLaWarps * kLaRows;                            // [4][16]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -80,27 +86,40 @@ latent_attn_mma_kernel(LaArgs a) {
         const int h = h0 + i / R;
         if (h < a.H) a.out[grow0 * a.ldo + (size_t)h * R + i % R] = __float2bfloat16_rn(0.f);
       }
+      if (a.nsplit > 1 && threadIdx.x < HB && h0 + threadIdx.x < a.H) {     // an empty range for the merge kernel
+        float* w = a.ws + (((size_t)s * a.H + h0 + threadIdx.x) * a.nsplit + blockIdx.z) * (R + 2);
+        w[R] = -INFINITY;
+        w[R + 1] = 0.f;
+      }
       return;
     }
   }
   const int kv_end = p0 + nq;
-  const int n_blk = (kv_end + kLaKeys - 1) / kLaKeys;
+  int blk_begin = 0, n_blk = (kv_end + kLaKeys - 1) / kLaKeys;
+  if (a.tile_seq == nullptr && a.nsplit > 1) {         // this CTA's range of key blocks (it may be empty)
+    const int per = (n_blk + a.nsplit - 1) / a.nsplit;
+    blk_begin = min(n_blk, (int)blockIdx.z * per);
+    n_blk = min(n_blk, blk_begin + per);
+  }
   const int32_t* bt = a.block_table + (size_t)s * a.max_blocks;
   const int cpr = W / 8;                               // 16-byte chunks per row
 
+  // a warp copies whole key rows (rows w, w + 4, ...): one page lookup per row, lanes take the row's 16-byte chunks
   auto issue = [&](int blk) {
-    uint8_t* dst = k_s + (blk & 1) * kLaKeys * pitch;
+    uint8_t* dst = k_s + (a.nbuf == 2 ? (blk & 1) : 0) * kLaKeys * pitch;
     const int k0 = blk * kLaKeys;
-    for (int ci = threadIdx.x; ci < kLaKeys * cpr; ci += blockDim.x) {
-      const int r = ci / cpr, c = ci - r * cpr;
+#pragma unroll 4
+    for (int r = warp; r < kLaKeys; r += kLaWarps) {
       const int key = k0 + r;
       const bool live = key < kv_end;
       const int kk = live ? key : 0;
-      const bf16* src = a.cache + ((size_t)bt[kk / a.page] * a.page + (kk % a.page)) * W + c * 8;
-      cp_async_16_zfill(dst + r * pitch + c * 16, src, live);
+      const int pg = kk >> a.page_shift;
+      const bf16* src = a.cache + ((size_t)__ldg(bt + pg) * a.page + (kk - (pg << a.page_shift))) * W;
+      uint8_t* d = dst + r * pitch;
+      for (int c = lane; c < cpr; c += 32) cp_async_16_zfill(d + c * 16, src + c * 8, live);
     }
   };
-  issue(0);
+  if (blk_begin < n_blk) issue(blk_begin);
   cp_async_commit();
 
   // ---- the 16 (row, head) pairs' absorbed queries
@@ -126,18 +145,24 @@ latent_attn_mma_kernel(LaArgs a) {
   const int ks_n = W / 16;
   const int col_chunk0 = warp * (R / 4) / 8;            // first 16-byte chunk of this warp's output columns
 
-  for (int blk = 0; blk < n_blk; ++blk) {
-    if (blk + 1 < n_blk) issue(blk + 1);
-    cp_async_commit();
-    cp_async_wait<1>();
+  const bool two = a.nbuf == 2;
+  for (int blk = blk_begin; blk < n_blk; ++blk) {
+    if (two) {
+      if (blk + 1 < n_blk) issue(blk + 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
     __syncthreads();                                    // block blk (and, first time, the queries) visible to all
-    const uint32_t k_base = smem_u32(k_s + (blk & 1) * kLaKeys * pitch);
+    const uint32_t k_base = smem_u32(k_s + (two ? (blk & 1) : 0) * kLaKeys * pitch);
 
     // S: 16 pairs x this warp's 16 keys
     float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
     {
       const uint32_t qa_addr = q_base + a_row * pitch + (ai >> 1) * 16;
       const uint32_t kb_addr = k_base + (warp * 16 + b_tok) * pitch + (ai & 1) * 16;
+#pragma unroll 4
       for (int ks = 0; ks < ks_n; ++ks) {
         uint32_t qf[4], b0, b1, b2, b3;
         ldsm_x4(qa_addr + ks * 32, qf[0], qf[1], qf[2], qf[3]);
@@ -210,6 +235,10 @@ latent_attn_mma_kernel(LaArgs a) {
       }
     }
     __syncthreads();                                    // this key buffer and the probability tile are free again
+    if (!two && blk + 1 < n_blk) {
+      issue(blk + 1);
+      cp_async_commit();
+    }
   }
   cp_async_wait<0>();
 
@@ -231,6 +260,21 @@ latent_attn_mma_kernel(LaArgs a) {
   }
   const int qi0 = r0 / HB, hh0 = h0 + r0 % HB, qi1 = r1 / HB, hh1 = h0 + r1 % HB;
   const bool ok0 = qi0 < nq && hh0 < a.H, ok1 = qi1 < nq && hh1 < a.H;
+  if (a.tile_seq == nullptr && a.nsplit > 1) {         // park (O, m, l) of this key range; the merge kernel finishes
+    const int cbs = warp * (R / 4) + 2 * (lane & 3);
+    float* w0 = a.ws + (((size_t)s * a.H + hh0) * a.nsplit + blockIdx.z) * (R + 2);
+    float* w1 = a.ws + (((size_t)s * a.H + hh1) * a.nsplit + blockIdx.z) * (R + 2);
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      if (ok0) { w0[cbs + t * 8] = o[t][0]; w0[cbs + t * 8 + 1] = o[t][1]; }
+      if (ok1) { w1[cbs + t * 8] = o[t][2]; w1[cbs + t * 8 + 1] = o[t][3]; }
+    }
+    if (warp == 0 && (lane & 3) == 0) {
+      if (ok0) { w0[R] = m0; w0[R + 1] = den0; }
+      if (ok1) { w1[R] = m1; w1[R + 1] = den1; }
+    }
+    return;
+  }
   if (a.sink != nullptr) {
     if (ok0) den0 += exp2f(a.sink[hh0] * 1.4426950408889634f - m0);
     if (ok1) den1 += exp2f(a.sink[hh1] * 1.4426950408889634f - m1);
@@ -248,9 +292,44 @@ latent_attn_mma_kernel(LaArgs a) {
   }
 }
 
-static size_t la_smem_bytes(int W) {
+// out[b][h] = sum_s O_s 2^(m_s - M) / (sum_s l_s 2^(m_s - M) + 2^(sink_h log2 e - M)),  M = max_s m_s; empty ranges
+// (m_s = -inf) are skipped.
+__global__ void __launch_bounds__(128)
+latent_attn_merge_kernel(const float* __restrict__ ws, const float* __restrict__ sink, bf16* out, int64_t ldo, int H,
+                         int R, int nsplit) {
+  const int b = blockIdx.x, h = blockIdx.y;
+  const float* p = ws + ((size_t)b * H + h) * nsplit * (R + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, p[(size_t)s * (R + 2) + R]);
+  float den = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float ms = p[(size_t)s * (R + 2) + R];
+    if (ms > -INFINITY) den += p[(size_t)s * (R + 2) + R + 1] * exp2f(ms - M);
+  }
+  if (sink != nullptr && M > -INFINITY) den += exp2f(sink[h] * 1.4426950408889634f - M);
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  for (int d = threadIdx.x; d < R; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float ms = p[(size_t)s * (R + 2) + R];
+      if (ms > -INFINITY) acc += p[(size_t)s * (R + 2) + d] * exp2f(ms - M);
+    }
+    out[(size_t)b * ldo + (size_t)h * R + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+static size_t la_smem_bytes(int W, int nbuf) {
   const size_t pitch = (size_t)W * 2 + 16;
-  return kLaRows * pitch + 2 * kLaKeys * pitch + kLaRows * kLaPPitch + 2 * kLaWarps * kLaRows * sizeof(float);
+  return kLaRows * pitch + nbuf * kLaKeys * pitch + kLaRows * kLaPPitch + 2 * kLaWarps * kLaRows * sizeof(float);
+}
+
+// two buffers while two CTAs still fit an SM's shared memory with them, else one
+static int la_nbuf(int W) { return la_smem_bytes(W, 2) <= 100 * 1024 ? 2 : 1; }
+
+static int la_log2(int v) {
+  int s = 0;
+  while ((1 << s) < v) ++s;
+  return s;
 }
 
 static int la_heads_per_cta(int H) {
@@ -261,7 +340,7 @@ static int la_heads_per_cta(int H) {
 
 template <int NT>
 static int la_launch(const LaArgs& a, dim3 grid, cudaStream_t s) {
-  const size_t smem = la_smem_bytes(a.W);
+  const size_t smem = la_smem_bytes(a.W, a.nbuf);
   static size_t attr = 0;
   if (smem > attr) {
     cudaError_t e = cudaFuncSetAttribute(latent_attn_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -298,7 +377,7 @@ extern "C" int b200_latent_attn_covers(int H, int R, int dr) {
   const int W = R + dr;
   if (H <= 0 || R <= 0 || dr < 0 || W % 16 != 0) return 0;
   if (!(R == 64 || R == 128 || R == 192 || R == 256 || R == 384 || R == 512)) return 0;
-  return la_smem_bytes(W) <= 220 * 1024 ? 1 : 0;
+  return la_smem_bytes(W, la_nbuf(W)) <= 220 * 1024 ? 1 : 0;
 }
 
 static int la_check(const void* qa, int64_t ldq, const void* cache, int64_t ldo, int H, int R, int dr) {
@@ -315,26 +394,52 @@ extern "C" int b200_latent_attn_prefill(const void* qa, int64_t ldq, const void*
                                         int n_tiles, int tile_rows, const float* sink, void* out, int64_t ldo, int H, int R,
                                         int dr, float scale, void* stream) {
   if (int rc = la_check(qa, ldq, cache, ldo, H, R, dr)) return rc;
-  B200_REQUIRE(tile_rows > 0 && tile_rows % kLaRows == 0 && page > 0, "latent_attn_prefill: tiles of %d rows (multiples of %d)",
+  B200_REQUIRE(tile_rows > 0 && tile_rows % kLaRows == 0, "latent_attn_prefill: tiles of %d rows (multiples of %d)",
                tile_rows, kLaRows);
+  B200_REQUIRE(page > 0 && (page & (page - 1)) == 0, "latent_attn_prefill: the page size %d is not a power of two", page);
   if (n_tiles <= 0) return B200_OK;
   const int hb = la_heads_per_cta(H);
   LaArgs a{(const bf16*)qa, ldq, (const bf16*)cache, page, block_table, max_blocks, cu_q, ctx_lens, tile_seq, tile_q0, nullptr,
-           sink, (bf16*)out, ldo, H, R + dr, R, hb, scale * 1.4426950408889634f};
+           sink, (bf16*)out, ldo, H, R + dr, R, hb, scale * 1.4426950408889634f, la_log2(page), 1, nullptr, la_nbuf(R + dr)};
   dim3 grid(n_tiles, (H + hb - 1) / hb, tile_rows / (kLaRows / hb));
   return la_dispatch(a, grid, (cudaStream_t)stream);
+}
+
+// Key ranges per row worth launching for B rows of H heads whose sequences are at most max_len long: enough CTAs for
+// two per SM, at least 256 keys per range, at most 16 ranges.
+extern "C" int b200_latent_attn_decode_splits(int B, int H, int max_len) {
+  const int hb = la_heads_per_cta(H);
+  const int ctas = B * ((H + hb - 1) / hb);
+  const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
+  int n = ctas > 0 ? (2 * sms) / ctas : 1;
+  const int by_len = (max_len + 255) / 256;
+  if (n > by_len) n = by_len;
+  if (n > 16) n = 16;
+  return n < 1 ? 1 : n;
+}
+
+extern "C" size_t b200_latent_attn_decode_workspace_bytes(int B, int H, int R, int nsplit) {
+  return nsplit > 1 ? (size_t)B * H * nsplit * (R + 2) * sizeof(float) : 0;
 }
 
 extern "C" int b200_latent_attn_decode(const void* qa, int64_t ldq, const void* cache, int page,
                                        const int32_t* block_table, int max_blocks, const int32_t* seq_lens, int B,
                                        const float* sink, void* out, int64_t ldo, int H, int R, int dr, float scale,
-                                       void* stream) {
+                                       int nsplit, void* workspace, void* stream) {
   if (int rc = la_check(qa, ldq, cache, ldo, H, R, dr)) return rc;
-  B200_REQUIRE(page > 0, "latent_attn_decode: bad page size");
+  B200_REQUIRE(page > 0 && (page & (page - 1)) == 0, "latent_attn_decode: the page size %d is not a power of two", page);
+  B200_REQUIRE(nsplit >= 1 && nsplit <= 16 && (nsplit == 1 || workspace != nullptr), "latent_attn_decode: %d key ranges need a workspace", nsplit);
   if (B <= 0) return B200_OK;
   const int hb = la_heads_per_cta(H);
   LaArgs a{(const bf16*)qa, ldq, (const bf16*)cache, page, block_table, max_blocks, nullptr, nullptr, nullptr, nullptr, seq_lens,
-           sink, (bf16*)out, ldo, H, R + dr, R, hb, scale * 1.4426950408889634f};
-  dim3 grid(B, (H + hb - 1) / hb, 1);
-  return la_dispatch(a, grid, (cudaStream_t)stream);
+           sink, (bf16*)out, ldo, H, R + dr, R, hb, scale * 1.4426950408889634f, la_log2(page), nsplit, (float*)workspace,
+           la_nbuf(R + dr)};
+  dim3 grid(B, (H + hb - 1) / hb, nsplit);
+  if (int rc = la_dispatch(a, grid, (cudaStream_t)stream)) return rc;
+  if (nsplit > 1) {
+    latent_attn_merge_kernel<<<dim3(B, H), 128, 0, (cudaStream_t)stream>>>((const float*)workspace, sink, (bf16*)out, ldo, H, R,
+                                                                          nsplit);
+    return b200_check_launch("b200_latent_attn_decode(merge)");
+  }
+  return B200_OK;
 }

@@ -68,6 +68,7 @@ moe_route_biased_kernel(const float* __restrict__ logits, int64_t ld, const floa
       const int oe = __shfl_xor_sync(0xffffffffu, be, o);
       if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; bs = os; }
     }
+    if (be >= E) { be = j; bs = 0.f; }                                 // logits that are not numbers: still a valid id
 #pragma unroll
     for (int i = 0; i < kRbPerLane; ++i)
       if (lane + 32 * i == be) c[i] = -CUDART_INF_F;                   // taken

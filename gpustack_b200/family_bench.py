@@ -1,6 +1,6 @@
-"""Side benchmark of the layer-list family (Vodavik) beside the closest Llama-class model of equal layer sizes.
+"""Side benchmark of the layer-list family (Vodavik, Danipel) beside the closest Llama-class model of equal layer sizes.
 
-`python bench.py --family vodavik` prints ONE JSON line (not the serving benchmark's line; that workload and its
+`python bench.py --family vodavik|danipel` prints ONE JSON line (not the serving benchmark's line; that workload and its
 contract are untouched).  Random weights, synthetic tokens.  Two kinds of numbers:
 
   model:   prefill tokens/s (prompts of `prompt` tokens, `seqs` at a time through runner.prefill) and decode tokens/s
@@ -21,7 +21,8 @@ import numpy as np
 import torch
 
 from . import ops
-from .config import (AttentionSpec, EngineConfig, LayerListConfig, LayerSpec, MLPSpec, MLSTMSpec, ModelConfig)
+from .config import (AttentionSpec, EngineConfig, LatentAttentionSpec, LayerListConfig, LayerSpec, MLPSpec, MLSTMSpec, ModelConfig,
+                     MoESpec, RotarySpec)
 
 ROOT = Path(__file__).resolve().parent.parent
 SIZES = {
@@ -29,6 +30,37 @@ SIZES = {
     "2k": (2048, 16, 4, 128, 8192, 32000),
     "4k": (4096, 32, 8, 128, 14336, 32000),
 }
+
+
+# Danipel at the same widths: latent 512 + 64 rotated (the cache row), heads 128 + 64 wide with 128-wide values, a
+# query latent of 3/8 of the width, 8 routed experts (2 chosen, 2 identity outputs) of a quarter of the dense
+# feed-forward's width each plus one shared expert of that width
+DANIPEL = {
+    # name: kv_rank, rot_dim, dim, vdim, q_rank, experts, top, identity, expert ff
+    "2k": (512, 64, 128, 128, 768, 8, 2, 2, 2048),
+    "4k": (512, 64, 128, 128, 1536, 8, 2, 2, 3584),
+}
+
+
+def danipel_config(size: str, layers: int = 4) -> LayerListConfig:
+    D, H, G, hd, ff, V = SIZES[size]
+    R, dr, dn, dv, qr, E, top, ident, ffe = DANIPEL[size]
+    specs = []
+    for i in range(layers):
+        two = i % 2 == 0
+        rot = RotarySpec(dims=dr, base=1e6, layout="half" if two else "interleaved", yarn_factor=0.0 if two else 8.0,
+                         yarn_original=4096.0, yarn_fast=32.0, yarn_slow=1.0)
+        mix = LatentAttentionSpec(heads=H, dim=dn, rot_dim=dr, vdim=dv, kv_rank=R, scale=(dn + dr) ** -0.5, rot=rot,
+                                  q_rank=qr if two else 0, sink=not two,
+                                  type_name="latent_attention_2" if two else "latent_attention")
+        if i in (0, layers - 1):
+            mlp = MLPSpec("dense", ff, act="gelu_tanh")
+        else:
+            mlp = MLPSpec("moe", ffe, act="clamped_swish",
+                          moe=MoESpec(experts=E, top=top, ff=ffe, limit=7.0, identity=ident, scale=2.5, shared_ff=ffe, shared_limit=7.0))
+        specs.append(LayerSpec(mix, mlp))
+    return LayerListConfig("Danipel", V, D, specs, norm_eps=1e-6, residual="streams", norm="tanh", streams=2,
+                           residual_mult=0.7, embed_scale=1.0)
 
 
 def _peaks():
@@ -270,16 +302,155 @@ def _kernel_numbers(size, T, B, ctx, log):
     return res
 
 
-def run(sizes=("2k", "4k"), seqs=4, prompt=2048, batch=64, decode_steps=32, log=None):
+def _kernel_numbers_danipel(size, T, B, ctx, log):
+    """Danipel's kernels beside the like kernels of the Llama-class path (dense and routed) at equal sizes."""
+    from .weights import _interleave_rows
+
+    D, H, G, hd, ff, V = SIZES[size]
+    R, dr, dn, dv, qr, E, top, ident, ffe = DANIPEL[size]
+    W = R + dr
+    hbm, flops_peak, how = _peaks()
+    flush = _Flush()
+    dev = "cuda"
+    bf, f32 = torch.bfloat16, torch.float32
+    rnd = lambda *s, dt=bf, sc=1.0: (torch.randn(*s, device=dev, dtype=f32) * sc).to(dt)   # noqa: E731
+    i32 = lambda x: torch.as_tensor(x, dtype=torch.int32, device=dev)   # noqa: E731
+    res = {}
+
+    def put(name, new_s, new_work, like_name, like_s, like_work, kind):
+        peak = hbm if kind == "bytes" else flops_peak
+        fn, fl = new_work / new_s / peak, like_work / like_s / peak
+        res[name] = {"us": round(new_s * 1e6, 1), "frac_of_" + how + "_" + kind: round(fn, 3), "like": like_name,
+                     "like_us": round(like_s * 1e6, 1), "like_frac": round(fl, 3), "distance_ratio": round(fl / fn, 2)}
+        log(f"  {name:34s} {new_s * 1e6:9.1f} us  {fn:6.3f} of roofline | {like_name}: {like_s * 1e6:9.1f} us {fl:6.3f}"
+            f"  -> {fl / fn:5.2f}x as far")
+
+    # ---- two residual streams: write-back + read + tanh norm in one pass, vs add + RMSNorm
+    S2 = 2
+    X = rnd(T, S2 * D, dt=f32)
+    y = rnd(T, D, dt=f32)
+    hc = rnd(2 * S2 + S2 * S2, dt=f32)
+    alpha, w, b = torch.full((1,), 0.5, device=dev), rnd(D), rnd(D)
+    xb = torch.empty(T, D, device=dev, dtype=bf)
+    t_new = _time(lambda: ops.streams_step(X, S2, y=y, hc_write=hc, mult=0.7, hc_read=hc, norm=(alpha, w, b), xb_out=xb), flush)
+    xr, rr = rnd(T, D), rnd(T, D)
+    t_like = _time(lambda: ops.fused_add_rms_norm(xr, rr, w, 1e-5, out=xr, residual_out=rr), flush)
+    put("streams_step (2 streams)", t_new, T * D * (S2 * 8.0 + 4 + 2), "fused_add_rms_norm", t_like, T * D * 8.0, "bytes")
+
+    # ---- latent norm + rotations + cache row vs rotation + page scatter
+    nblk = (B * ctx + T) // 16 + 8
+    proj = rnd(T, H * (dn + dr) + W)
+    cache = rnd(nblk, 1, 16, W)
+    qa = torch.empty(T, H * W, device=dev, dtype=bf)
+    pos, slots = i32(np.arange(T) % 4096), i32(np.arange(T))
+    freq = torch.tensor(RotarySpec(dims=dr, base=1e6).frequencies()[0], dtype=torch.float64, device=dev)
+    kvw = rnd(R)
+    t_new = _time(lambda: ops.latent_prep(proj, H * (dn + dr), proj[:, :H * (dn + dr)], kvw, pos, slots, cache, qa, H, dn, dr, R, dr,
+                                          False, freq, 1.0, 1e-6), flush)
+    qkv = rnd(T, (H + 2 * G) * hd)
+    kc, vc = rnd(nblk, G, 16, hd), rnd(nblk, G, 16, hd)
+    cs = rnd(8192, hd)
+    t_like = _time(lambda: ops.rope_kv_write(qkv, pos, cs, kc, vc, slots, H, G, hd), flush)
+    put("latent_prep", t_new, T * (W + H * dr) * 4.0, "rope_kv_write", t_like, T * (H + 2 * G) * hd * 4.0, "bytes")
+
+    # ---- per-head absorption of W_uk into the queries / W_uv after the attention vs one plain GEMM
+    ukt = rnd(H, R, dn, sc=0.05)
+    t_new = _time(lambda: ops.head_linear(proj, ukt, qa, H, n=R, k=dn, x_head=dn + dr, out_head=W), flush)
+    wq = rnd((H + 2 * G) * hd, D, sc=0.02)
+    xin = rnd(T, D)
+    t_like = _time(lambda: ops.gemm(xin, wq, out=qkv), flush)
+    put("query absorption (H GEMMs)", t_new, 2.0 * T * H * dn * R, "qkv GEMM", t_like, 2.0 * T * (H + 2 * G) * hd * D, "flops")
+    o_lat = rnd(T, H * R)
+    uv = rnd(H * dv, R, sc=0.05)
+    mo = torch.empty(T, H * dv, device=dev, dtype=bf)
+    t_new = _time(lambda: ops.head_linear(o_lat, uv, mo, H, n=dv, k=R, x_head=R, out_head=dv), flush)
+    put("value expansion (H GEMMs)", t_new, 2.0 * T * H * dv * R, "qkv GEMM", t_like, 2.0 * T * (H + 2 * G) * hd * D, "flops")
+
+    # ---- attention over the latent cache vs the Llama-class kernels
+    Sq = max(1, T // 2048)
+    L = T // Sq
+    nb = (L + 15) // 16
+    bt = i32(np.arange(Sq * nb).reshape(Sq, nb) + 1)
+    cu, ctx0 = i32(np.arange(Sq + 1) * L), i32(np.zeros(Sq))
+    ts_, tq_ = ops.build_prefill_tiles([L] * Sq, ops.attn_sink_prefill_tile(), [0] * Sq)
+    ts_d, tq_d = i32(ts_), i32(tq_)
+    sink = rnd(H, dt=f32)
+    t_new = _time(lambda: ops.latent_attn_prefill(qa, cache, bt, cu, ctx0, ts_d, tq_d, sink, o_lat, H, R, dr, W ** -0.5), flush,
+                  iters=5, warm=2)
+    tile = ops.attn_prefill_tile(H, G)
+    tl, tql = ops.build_prefill_tiles([L] * Sq, tile, [0] * Sq)
+    tl, tql = i32(tl), i32(tql)
+    out = torch.empty(T, H * hd, device=dev, dtype=bf)
+    t_like = _time(lambda: ops.paged_attn_prefill(qkv, qkv.shape[1], kc, vc, bt, cu, ctx0, tl, tql, out, H, G, hd, hd ** -0.5), flush)
+    pairs = Sq * (L * L / 2)
+    put("latent attention prefill", t_new, 2.0 * pairs * H * (W + R), "paged_attn_prefill tc", t_like, 4.0 * pairs * H * hd, "flops")
+    nbd = (ctx + 16) // 16
+    btd = i32(np.arange(B * nbd).reshape(B, nbd) % (nblk - 1) + 1)
+    lens = i32(np.full(B, ctx))
+    qaB, olB = qa[:B], o_lat[:B]
+    lsp = ops.latent_attn_decode_splits(B, H, ctx + 16)
+    lws = ops.latent_attn_decode_workspace(B, H, R, 16, dev)
+    t_new = _time(lambda: ops.latent_attn_decode(qaB, cache, btd, lens, sink, olB, H, R, dr, W ** -0.5, num_splits=lsp,
+                                                 workspace=lws), flush)
+    splits = ops.attn_decode_splits(B, G, ctx + 16)
+    ws = ops.attn_decode_workspace(B, H, hd, splits, dev)
+    outd = torch.empty(B, H * hd, device=dev, dtype=bf)
+    qB = qkv[:B]
+    t_like = _time(lambda: ops.paged_attn_decode(qB, qkv.shape[1], kc, vc, btd, lens, outd, H, G, hd, hd ** -0.5,
+                                                 num_splits=splits, workspace=ws), flush)
+    put("latent attention decode", t_new, B * ctx * W * 2.0, "paged_attn_decode", t_like, B * ctx * G * hd * 4.0, "bytes")
+    res["latent attention decode"]["tflops"] = round(2.0 * B * ctx * H * (W + R) / t_new / 1e12, 1)
+
+    # ---- gated feed-forward: activation in the GEMM's epilogue
+    wgu = rnd(2 * ff, D, sc=0.02)
+    au = torch.empty(T, ff, device=dev, dtype=bf)
+    t_new = _time(lambda: ops.gated_linear(xin, wgu, au, "gelu_tanh"), flush)
+    t_like = _time(lambda: ops.gemm_silu_mul(xin, wgu, out=au), flush)
+    put("gate_up GEMM + GELU*mul", t_new, 4.0 * T * ff * D, "gate_up GEMM + SiLU*mul", t_like, 4.0 * T * ff * D, "flops")
+
+    # ---- routed experts (router, choice, pair grouping, grouped GEMMs, combine) vs the Mixtral path at equal sizes
+    for rows, tag in ((T, "prefill"), (B, "decode")):
+        rws = ops.RoutedWorkspace(rows, top, E + ident, D, ffe, bf, dev)
+        router, corr = torch.zeros(128, D, device=dev, dtype=bf), rnd(E + ident, dt=f32, sc=0.01)
+        router[:E + ident] = rnd(E + ident, D, sc=0.05)          # zero rows up to a weight tile, as the loader stores it
+        w13 = rnd(E * 2 * ffe, D, sc=0.02)
+        w2 = rnd(E * D, ffe, sc=0.02)
+        xr_ = xin[:rows]
+        yo = torch.empty(rows, D, device=dev, dtype=f32)
+        t_new = _time(lambda: ops.routed_experts(xr_, router, corr, w13, w2, rws, yo, E, ident, top, 2.5, ffe, 7.0), flush,
+                      iters=5, warm=2)
+        mws = ops.MoEWorkspace(rows, top, E, D, ffe, dev)
+        rl = rnd(rows, ops.ROUTER_PAD)
+        rw_ = ops.pad_router(router[:E].contiguous())
+        yb = torch.empty(rows, D, device=dev, dtype=bf)
+
+        def like():
+            ops.gemm(xr_, rw_, out=rl)
+            ops.moe_experts(xr_, rl, w13, w2, top, mws, out=yb)
+
+        t_like = _time(like, flush, iters=5, warm=2)
+        # identity outputs take a share of the pairs: count the expert products of an even spread
+        share = E / (E + ident)
+        put(f"routed experts ({tag})", t_new, 6.0 * rows * top * share * D * ffe, f"Mixtral experts ({tag})", t_like,
+            6.0 * rows * top * D * ffe, "flops")
+        del rws, mws
+    return res
+
+
+FAMILIES = {"vodavik": (vodavik_config, _kernel_numbers), "danipel": (danipel_config, _kernel_numbers_danipel)}
+
+
+def run(sizes=("2k", "4k"), seqs=4, prompt=2048, batch=64, decode_steps=32, log=None, family="vodavik"):
     log = log or (lambda m: print(m, file=sys.stderr, flush=True))
     hbm, fl, how = _peaks()
-    out = {"bench": "family", "family": "vodavik", "dtype": "bf16", "data": "synthetic", "peaks": how,
+    make, kernels = FAMILIES[family]
+    out = {"bench": "family", "family": family, "dtype": "bf16", "data": "synthetic", "peaks": how,
            "workload": {"prefill": f"{seqs} x {prompt}", "decode": f"{batch} rows at context {prompt}", "layers": 4}, "sizes": {}}
     for size in sizes:
         log(f"size {size}: {SIZES[size]}")
         o = {"model": {}, "kernels": {}}
-        for name, cfg in (("vodavik", vodavik_config(size)), ("llama", llama_config(size))):
+        for name, cfg in ((family, make(size)), ("llama", llama_config(size))):
             o["model"][name] = _model_numbers(cfg, seqs, prompt, batch, decode_steps, log)
-        o["kernels"] = _kernel_numbers(size, seqs * prompt, batch, prompt, log)
+        o["kernels"] = kernels(size, seqs * prompt, batch, prompt, log)
         out["sizes"][size] = o
     return out

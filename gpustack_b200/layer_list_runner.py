@@ -209,6 +209,17 @@ class LayerListRunner(ModelRunner):
             self._dec_ws[key] = torch.zeros((need + 3) // 4, dtype=torch.float32, device=self.device)
         return splits, self._dec_ws[key]
 
+    def _latent_decode_plan(self, B: int, m):
+        """(key ranges, workspace) of the latent decode attention for B rows of mixer m; one workspace per shape, sized
+        for the largest batch and the most ranges."""
+        if self.act_dtype != BF16 or not ops.latent_attn_covers(m.heads, m.kv_rank, m.rot_dim):
+            return 1, None
+        splits = ops.latent_attn_decode_splits(B, m.heads, self.max_model_len)
+        key = ("latent", m.heads, m.kv_rank)
+        if key not in self._dec_ws:
+            self._dec_ws[key] = ops.latent_attn_decode_workspace(self.max_seqs, m.heads, m.kv_rank, 16, self.device)
+        return splits, self._dec_ws[key]
+
     def _run_layers(self, T: int, Tp: int, Bd: int, nt: int, bt_p, cu_p, ctx_p, ts, tq, lens_d, bt_d, cu_all, ctx_all,
                     slots_all) -> None:
         """Rows [0, Tp): prompt portions (tiles ts / tq over cu_p / ctx_p / bt_p); rows [Tp, T): Bd single new
@@ -287,7 +298,9 @@ class LayerListRunner(ModelRunner):
             ops.latent_attn_prefill(qa[:Tp], cache, bt_p, cu_p, ctx_p, ts, tq, lw.sink, o_lat[:Tp], H, R, dr, m.scale,
                                     tile_rows=self.prefill_tile)
         if Bd:
-            ops.latent_attn_decode(qa[Tp:T], cache, bt_d, lens_d, lw.sink, o_lat[Tp:T], H, R, dr, m.scale)
+            splits, ws = self._latent_decode_plan(Bd, m)
+            ops.latent_attn_decode(qa[Tp:T], cache, bt_d, lens_d, lw.sink, o_lat[Tp:T], H, R, dr, m.scale, num_splits=splits,
+                                   workspace=ws)
         ops.head_linear(o_lat, lw.uv, out, H, n=dv, k=R, x_head=R, out_head=dv)
         self.stats["kernel_launches"] += 3 + (1 if nt else 0) + (1 if Bd else 0)
 

@@ -440,7 +440,7 @@ def _cuda(*ts) -> None:
             raise B200Error("expected CUDA tensors (there is no CPU path)")
 
 
-def linear(x, w, out, bias=None, relu2: bool = False):
+def linear(x, w, out, bias=None, relu2: bool = False, force_simt: bool = False):
     """out = x @ w.T (+ bias); relu2: out = max(., 0)^2 (in the GEMM's epilogue on the tensor-core path).  bf16 x / bf16 or fp32 out with K a multiple of 64 and 16-byte aligned rows
     go to the tcgen05 GEMM; every other case (fp32 activations = a model served in true 32-bit; odd
     shapes) runs on the CUDA cores with fp32 FMA accumulation."""
@@ -450,7 +450,7 @@ def linear(x, w, out, bias=None, relu2: bool = False):
     M, K = x.shape
     N = w.shape[0]
     xf, yf = _is_f32(x), _is_f32(out)
-    if (not xf and bias is None and K % 64 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+    if (not force_simt and not xf and bias is None and K % 64 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
             and (out.stride(0) * out.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0
             and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
         if not relu2:
@@ -641,13 +641,26 @@ def latent_attn_prefill(qa, cache, block_table, cu_q, ctx_lens, tile_seq, tile_q
                              scale, tile_rows=tile_rows, v_ld=R + dr)
 
 
-def latent_attn_decode(qa, cache, block_table, seq_lens, sink, out, H, R, dr, scale):
-    """The same for one new row per sequence (row b sees keys [0, seq_lens[b]))."""
-    _cuda(qa, cache, block_table, seq_lens, sink, out)
+def latent_attn_decode_splits(B: int, H: int, max_len: int) -> int:
+    return load().b200_latent_attn_decode_splits(B, H, max_len)
+
+
+def latent_attn_decode_workspace(B: int, H: int, R: int, num_splits: int, device) -> Optional[torch.Tensor]:
+    n = load().b200_latent_attn_decode_workspace_bytes(B, H, R, num_splits)
+    return torch.empty((n + 3) // 4, dtype=torch.float32, device=device) if n else None
+
+
+def latent_attn_decode(qa, cache, block_table, seq_lens, sink, out, H, R, dr, scale, num_splits: int = 1, workspace=None):
+    """The same for one new row per sequence (row b sees keys [0, seq_lens[b])).  num_splits > 1 (tensor-core kernel
+    only): the keys of every row are cut into that many ranges, merged by a second launch."""
+    _cuda(qa, cache, block_table, seq_lens, sink, out, workspace)
     if qa.dtype == torch.bfloat16 and latent_attn_covers(H, R, dr) and qa.stride(0) % 8 == 0 and qa.data_ptr() % 16 == 0:
+        if workspace is None:
+            num_splits = 1
         check(load().b200_latent_attn_decode(_p(qa), qa.stride(0), _p(cache), cache.shape[2], _p(block_table),
                                              block_table.shape[1], _p(seq_lens), seq_lens.shape[0], _p(sink), _p(out),
-                                             out.stride(0), H, R, dr, scale, _stream()), "latent_attn_decode")
+                                             out.stride(0), H, R, dr, scale, num_splits, _p(workspace), _stream()),
+              "latent_attn_decode")
         return out
     return attn_sink_decode(qa, -1, cache, cache, block_table, seq_lens, sink, out, H, 1, R + dr, R, scale, v_ld=R + dr)
 
@@ -670,9 +683,10 @@ def linear_simt_grouped(x, w, out, M, N, K, ldx, ldw, ldy, batch=1, bsx=0, bsw=0
 
 def head_linear(x, w, out, H: int, n: int, k: int, x_head: int, out_head: int):
     """Per-head linear: out[t, h*out_head : +n] = w[h] (n x k, contiguous) @ x[t, h*x_head : +k] for every head.
-    bf16 with k a multiple of 64 and 16-byte aligned head slices: one tcgen05 GEMM per head over strided views;
-    otherwise ONE batched CUDA-core launch."""
-    if (x.dtype == torch.bfloat16 and H <= TC_HEAD_LINEAR_MAX_HEADS and _tc_gemm_ok(x, w, out, k) and x_head % 8 == 0 and (n * k) % 8 == 0
+    bf16 prompt-sized steps with k a multiple of 64 and 16-byte aligned head slices: one tcgen05 GEMM per head over
+    strided views; otherwise ONE batched CUDA-core launch."""
+    if (x.dtype == torch.bfloat16 and x.shape[0] > TC_HEAD_LINEAR_MIN_ROWS and H <= TC_HEAD_LINEAR_MAX_HEADS
+            and _tc_gemm_ok(x, w, out, k) and x_head % 8 == 0 and (n * k) % 8 == 0
             and (out_head * out.element_size()) % 16 == 0):
         w3 = w.view(H, n, k)
         for h in range(H):
@@ -683,6 +697,7 @@ def head_linear(x, w, out, H: int, n: int, k: int, x_head: int, out_head: int):
 
 
 TC_HEAD_LINEAR_MAX_HEADS = 128
+TC_HEAD_LINEAR_MIN_ROWS = 256      # decode-sized steps: ONE batched CUDA-core launch beats H short tensor-core launches
 
 
 def _tc_gemm_ok(x, w, out, K) -> bool:
@@ -733,7 +748,7 @@ class RoutedWorkspace:
         self.capacity = max(moe_capacity_rows(n_pairs, e_total, bx) for bx in (32, 64, 128, 256))
         self.xp = None            # gathered input rows of the tensor-core path, allocated at its first use
         i32 = lambda *s: torch.empty(*s, dtype=torch.int32, device=device)   # noqa: E731
-        self.logits = torch.empty(max_tokens, e_total, dtype=torch.float32, device=device)
+        self.logits = torch.empty(max_tokens, -(-e_total // 128) * 128, dtype=torch.float32, device=device)
         self.topk_ids, self.topk_w = i32(n_pairs), torch.empty(n_pairs, dtype=torch.float32, device=device)
         self.pair_row, self.row_pair = i32(n_pairs), i32(self.capacity)
         self.row_weight = torch.empty(self.capacity, dtype=torch.float32, device=device)
@@ -763,7 +778,8 @@ def routed_experts(x, router, correction, w13, w2, ws: RoutedWorkspace, out, n_r
         raise B200Error(f"routed_experts: {T} tokens exceed the workspace ({ws.capacity} rows)")
     L, st = load(), _stream()
     lg = ws.logits[:T]
-    linear(x, router, lg)                                           # fp32 logits
+    # fp32 logits; a router padded to whole weight tiles (weights.load_layer_list) takes the tensor-core GEMM in bf16
+    linear(x, router, lg, force_simt=router.shape[0] % 128 != 0)
     moe_route_biased(lg, correction, top_k, scale, ws.topk_ids, ws.topk_w, E)
     check(L.b200_moe_align(_p(ws.topk_ids), _p(ws.topk_w), n_pairs, E, bx, cap, _p(ws.pair_row), _p(ws.row_pair),
                            _p(ws.row_weight), _p(ws.tile_expert), _p(ws.num_tiles), st), "moe_align")

@@ -369,7 +369,7 @@ class LayerListLayer:
     # gated feed-forward: gate_up rows interleaved (2i = gate_i, 2i+1 = up_i), `up` above is unused
     gate_up: Optional[torch.Tensor] = None       # [2 ff, D]
     # routed feed-forward
-    router: Optional[torch.Tensor] = None        # [experts + identity, D]
+    router: Optional[torch.Tensor] = None        # [experts + identity rounded up to 128, D], zero rows behind the outputs
     correction: Optional[torch.Tensor] = None    # fp32 [experts + identity]
     w13: Optional[torch.Tensor] = None           # [experts * 2 ff, D], per expert interleaved gate / up rows
     w2: Optional[torch.Tensor] = None            # [experts * D, ff]
@@ -541,7 +541,11 @@ def load_layer_list(cfg, get: Callable[[str], torch.Tensor], device: str) -> Lay
                 lw.hc2 = hyper(p + "hc2")
             if layer.mlp.kind == "moe":
                 e = layer.mlp.moe
-                lw.router, lw.correction = g(p + "mlp.router"), f32(p + "mlp.correction")
+                # zero rows up to a whole GEMM weight tile: the router projection is an ordinary one-tile product
+                router = g(p + "mlp.router")
+                lw.router = torch.zeros(-(-router.shape[0] // 128) * 128, router.shape[1], dtype=BF16, device=device)
+                lw.router[:router.shape[0]] = router
+                lw.correction = f32(p + "mlp.correction")
                 lw.w13 = torch.cat([_interleave_rows(g(p + f"mlp.e{i}.gate"), g(p + f"mlp.e{i}.up"))
                                     for i in range(e.experts)], dim=0).contiguous()
                 lw.w2 = torch.cat([g(p + f"mlp.e{i}.down") for i in range(e.experts)], dim=0).contiguous()

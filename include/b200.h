@@ -342,9 +342,13 @@ int b200_latent_attn_prefill(const void* qa, int64_t ldq, const void* cache, int
                              int max_blocks, const int32_t* cu_q, const int32_t* ctx_lens, const int32_t* tile_seq,
                              const int32_t* tile_q0, int n_tiles, int tile_rows, const float* sink, void* out,
                              int64_t ldo, int H, int R, int dr, float scale, void* stream);
+/* decode: nsplit > 1 cuts every row's keys into that many ranges (more CTAs for small batches of long sequences) and
+ * merges them in a second launch; workspace of b200_latent_attn_decode_workspace_bytes(), contents irrelevant. */
+int b200_latent_attn_decode_splits(int B, int H, int max_len);
+size_t b200_latent_attn_decode_workspace_bytes(int B, int H, int R, int nsplit);
 int b200_latent_attn_decode(const void* qa, int64_t ldq, const void* cache, int page, const int32_t* block_table,
                             int max_blocks, const int32_t* seq_lens, int B, const float* sink, void* out, int64_t ldo,
-                            int H, int R, int dr, float scale, void* stream);
+                            int H, int R, int dr, float scale, int nsplit, void* workspace, void* stream);
 /* Batched / grouped / gated linear on the CUDA cores (see gemm_simt_grouped.cu).  act: 0 plain, 1 gelu_tanh(g) u,
  * 2 clamped g sigmoid(1.702 g) (u + 1) with `limit`, 3 silu(g) u; act != 0: W rows interleaved gate / up, N pairs. */
 int b200_linear_simt_grouped(const void* X, int x_f32, const void* W, void* Y, int y_f32, int M, int N, int K,

@@ -101,7 +101,7 @@ def test_weight_fusion_layout_and_checkpoint_round_trip(tmp_path):
         and torch.equal(hc[6:].view(3, 3), sd["l0.hc1.mix"].float())
     assert a.norm1_alpha.shape == (1,) and torch.equal(a.norm1_b, sd["l0.norm1.b"])
     assert torch.equal(a.w13[0::2][:18], sd["l0.mlp.e0.gate"]) and torch.equal(a.w13[1::2][18:36], sd["l0.mlp.e1.up"])
-    assert torch.equal(a.w2[52:104], sd["l0.mlp.e1.down"]) and a.router.shape == (7, 52) and a.correction.dtype == torch.float32
+    assert torch.equal(a.w2[52:104], sd["l0.mlp.e1.down"]) and a.router.shape == (128, 52) and torch.equal(a.router[:7], sd["l0.mlp.router"]) and not bool(a.router[7:].any()) and a.correction.dtype == torch.float32
     assert torch.equal(a.shared13[0::2], sd["l0.mlp.shared.gate"]) and torch.equal(a.shared2, sd["l0.mlp.shared.down"])
     g = w.layers[2]
     assert torch.equal(g.gate_up[0::2], sd["l2.mlp.gate"]) and torch.equal(g.gate_up[1::2], sd["l2.mlp.up"]) and g.up is None

@@ -392,6 +392,15 @@ def test_attention_over_the_latent_cache_prefill_and_decode(dtype, H, R, dr, sin
     ops.latent_attn_decode(qd[rows + [0]].contiguous(), cache, bt4, i32([ctx + r + 1 for r in rows] + [0]), skd, o4, H, R, dr, scale)
     assert _rel(o4[:len(rows)].view(len(rows), H, R).float(), want[rows]) < tol
     assert bool(torch.isfinite(o4[-1].float()).all())
+    if dtype == BF and ops.latent_attn_covers(H, R, dr):       # the keys cut into ranges (some of them empty) and merged
+        for ns in (2, 3, 16):
+            ws = ops.latent_attn_decode_workspace(len(rows) + 1, H, R, 16, "cuda")
+            ws.fill_(float("nan"))
+            o5 = torch.zeros_like(o4)
+            ops.latent_attn_decode(qd[rows + [0]].contiguous(), cache, bt4, i32([ctx + r + 1 for r in rows] + [0]), skd, o5, H, R, dr, scale,
+                                   num_splits=ns, workspace=ws)
+            assert _rel(o5[:len(rows)].view(len(rows), H, R).float(), want[rows]) < tol, ns
+            assert bool((o5[-1] == 0).all())
 
 
 @pytest.mark.parametrize("kernel", ["prefill", "decode"])
