@@ -271,7 +271,7 @@ def parity_probe(a, rank, world):
     for max_seqs in (8, 256):
         sd = random_state_dict(mcfg, seed=7, device=device)
         if rank == 0 and oracle is None:
-            from oracle import llama_oracle as O   # the checker; never on the timed path
+            from oracle import llama_oracle as O   # the plain restatement; never on the timed path
 
             oc = O.LlamaConfig(vocab_size=mcfg.vocab_size, hidden_size=mcfg.hidden_size,
                                intermediate_size=mcfg.intermediate_size, num_hidden_layers=mcfg.num_hidden_layers,

@@ -701,8 +701,8 @@ static int launch_gemm_mc(const CUtensorMap& tw, const CUtensorMap& tx, void* Y,
 // streams past once per group (B200_GEMM_GROUP_M overrides for experiments).  16 tiles measured best
 // on the K = 4096 prefill shapes (16 x 256 tokens x 8 KB = 32 MB of activations); for long K the
 // group is shrunk so that its activation rows stay below ~64 MB -- a 16-tile group of the down
-// projection (K = 14336) is 117 MB, does not fit the 126 MB L2 next to the weights, and round 1
-// measured 3.1x the algorithmic DRAM traffic for it.
+// projection (K = 14336) is 117 MB, does not fit the 126 MB L2 next to the weights, and was
+// measured at 3.1x the algorithmic DRAM traffic.
 static int gemm_group_m(int m_tiles, int K) {
   static int v = -1;
   if (v < 0) {
@@ -940,6 +940,22 @@ extern "C" int b200_gemm_bf16_silu_mul(const void* X, const void* W, void* Y, in
     case 128: return launch_gemm<128, 1>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, 1, s);
     default: return launch_gemm<256, 1>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, 1, s);
   }
+}
+
+// One GEMM per head over strided views of wider rows: Y[:, h * y_head : + N] = X[:, h * x_head : + K] W_h^T with W_h the
+// h-th contiguous [N, K] matrix.  The loop runs here so that a step pays one library call for all heads.
+extern "C" int b200_gemm_bf16_heads(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx,
+                                    int64_t ldy, int H, int64_t x_head, int64_t y_head, int out_f32, void* stream) {
+  B200_REQUIRE(H >= 1, "gemm_heads: bad head count %d", H);
+  const size_t es = out_f32 ? 4 : 2;
+  for (int h = 0; h < H; ++h) {
+    const int rc = b200_gemm_bf16_ex(reinterpret_cast<const bf16*>(X) + (size_t)h * x_head,
+                                     reinterpret_cast<const bf16*>(W) + (size_t)h * N * K,
+                                     reinterpret_cast<uint8_t*>(Y) + (size_t)h * y_head * es, M, N, K, ldx, K, ldy,
+                                     out_f32 ? 1 : 0, 1, 0, stream);
+    if (rc != B200_OK) return rc;
+  }
+  return B200_OK;
 }
 
 // act(x gate^T) (*) (x up^T) over interleaved gate / up rows, bf16 out [M, N/2]; act / limit as gated_pair() above.

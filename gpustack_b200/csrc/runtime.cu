@@ -63,9 +63,9 @@ bool pdl_enabled() {
 bool pdl_class_enabled(int cls) {
   static int off = -1;
   if (off < 0) {
-    // Every class is a programmatic dependent by default.  (Round 1 had to serialise the MoE class:
-    // with the entry-time trigger, CUDA-graph replays of the tiny Mixtral decode step computed wrong
-    // logits -- DESIGN.md section 9.  The late trigger in common.cuh removes the cause; the knob
+    // Every class is a programmatic dependent by default.  (With an entry-time trigger the MoE class had to be
+    // serialised: CUDA-graph replays of the tiny Mixtral decode step computed wrong logits.  The late
+    // trigger in common.cuh removes the cause; the knob
     // B200_PDL_OFF_CLASSES=<bitmask> stays for experiments.)
     const char* e = getenv("B200_PDL_OFF_CLASSES");
     off = e ? atoi(e) : 0;

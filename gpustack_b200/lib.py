@@ -106,6 +106,7 @@ SIGNATURES = {
                                        _i32, _vp, _vp]),
     "b200_latent_attn_decode_splits": (_i32, [_i32, _i32, _i32]),
     "b200_latent_attn_decode_workspace_bytes": (_sz, [_i32, _i32, _i32, _i32]),
+    "b200_gemm_bf16_heads": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i32, _i64, _i64, _i32, _vp]),
     "b200_gemm_bf16_gated": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i64, _i64, _i64, _i32, _f32, _vp]),
     "b200_moe_grouped_gemm_ex": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i64, _i64, _i64, _vp, _vp, _vp, _i32, _i32,
                                         _i32, _f32, _i32, _vp]),

@@ -688,9 +688,10 @@ def head_linear(x, w, out, H: int, n: int, k: int, x_head: int, out_head: int):
     if (x.dtype == torch.bfloat16 and x.shape[0] > TC_HEAD_LINEAR_MIN_ROWS and H <= TC_HEAD_LINEAR_MAX_HEADS
             and _tc_gemm_ok(x, w, out, k) and x_head % 8 == 0 and (n * k) % 8 == 0
             and (out_head * out.element_size()) % 16 == 0):
-        w3 = w.view(H, n, k)
-        for h in range(H):
-            gemm(x[:, h * x_head:h * x_head + k], w3[h], out=out[:, h * out_head:h * out_head + n], out_dtype=out.dtype)
+        if not w.is_contiguous():
+            raise B200Error("head_linear: the per-head matrices must be contiguous")
+        check(load().b200_gemm_bf16_heads(_p(x), _p(w), _p(out), x.shape[0], n, k, x.stride(0), out.stride(0), H, x_head,
+                                          out_head, _is_f32(out), _stream()), "gemm_heads")
         return out
     return linear_simt_grouped(x, w, out, x.shape[0], n, k, x.stride(0), k, out.stride(0), batch=H, bsx=x_head, bsw=n * k,
                                bsy=out_head)

@@ -356,6 +356,9 @@ int b200_linear_simt_grouped(const void* X, int x_f32, const void* W, void* Y, i
                              const int32_t* row_pair, int top_k, const int32_t* tile_expert, const int32_t* num_tiles,
                              int n_real, int64_t w_expert, const float* row_scale, int act, float limit, void* stream);
 int b200_simt_group_rows(void);
+/* H GEMMs over strided views: Y[:, h*y_head : +N] = X[:, h*x_head : +K] W_h^T, W_h the h-th contiguous [N, K] matrix. */
+int b200_gemm_bf16_heads(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx, int64_t ldy, int H,
+                         int64_t x_head, int64_t y_head, int out_f32, void* stream);
 /* The tcgen05 GEMM with a gated epilogue over interleaved gate / up rows (bf16 Y [M, N/2], K % 64 == 0):
  * act 0 silu(g) u (factors rounded to bf16), 1 gelu_tanh(g) u, 2 clamped g sigmoid(1.702 g) (u + 1). */
 int b200_gemm_bf16_gated(const void* X, const void* W, void* Y, int M, int N, int K, int64_t ldx, int64_t ldw,
