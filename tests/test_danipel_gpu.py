@@ -358,7 +358,8 @@ def _latent_case(dtype, n_keys, page, H, R, dr, seed, perm=True):
 
 @pytest.mark.parametrize("dtype", [torch.float32, BF])
 @pytest.mark.parametrize("H,R,dr,sink", [(3, 20, 6, True), (16, 128, 64, False), (1, 256, 8, True), (20, 512, 64, True),
-                                         (3, 64, 16, False), (8, 192, 32, True), (2, 384, 32, False)])
+                                         (3, 64, 16, False), (8, 192, 32, True), (2, 384, 32, False), (2, 192, 16, True),
+                                         (32, 128, 32, False), (40, 64, 32, True)])
 def test_attention_over_the_latent_cache_prefill_and_decode(dtype, H, R, dr, sink):
     """Absorbed form: every head scores against the same cache rows and takes their first R entries as values.
     A portion of 37 rows after 130 cached tokens (three 64-key blocks, ten pages), then single rows, against the
