@@ -14,6 +14,9 @@ import torch
 from .lib import B200Error, check, load
 
 BLOCK_SIZE = 16  # tokens per KV page (vLLM default block_size)
+# A/B switch: B200_LAYER_LIST_TC=0 keeps the layer-list families off the tensor cores (every product on the CUDA-core
+# kernels, attention on the generic kernels) -- to tell a rounding effect from a fault of a tensor-core route
+LAYER_LIST_TC = __import__("os").environ.get("B200_LAYER_LIST_TC", "1") != "0"
 
 
 class KernelTimer:
@@ -450,7 +453,7 @@ def linear(x, w, out, bias=None, relu2: bool = False, force_simt: bool = False):
     M, K = x.shape
     N = w.shape[0]
     xf, yf = _is_f32(x), _is_f32(out)
-    if (not force_simt and not xf and bias is None and K % 64 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+    if (LAYER_LIST_TC and not force_simt and not xf and bias is None and K % 64 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
             and (out.stride(0) * out.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0
             and w.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
         if not relu2:
@@ -622,7 +625,7 @@ def latent_prep(proj, kv_col: int, q, kv_norm_w, positions, slots, cache, qa, H,
 
 
 def latent_attn_covers(H: int, R: int, dr: int) -> bool:
-    return bool(load().b200_latent_attn_covers(H, R, dr))
+    return LAYER_LIST_TC and bool(load().b200_latent_attn_covers(H, R, dr))
 
 
 def latent_attn_prefill(qa, cache, block_table, cu_q, ctx_lens, tile_seq, tile_q0, sink, out, H, R, dr, scale,
@@ -702,7 +705,7 @@ TC_HEAD_LINEAR_MIN_ROWS = 256      # decode-sized steps: ONE batched CUDA-core l
 
 
 def _tc_gemm_ok(x, w, out, K) -> bool:
-    return (x.dtype == torch.bfloat16 and K % 64 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+    return (LAYER_LIST_TC and x.dtype == torch.bfloat16 and K % 64 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
             and (out.stride(0) * out.element_size()) % 16 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
             and out.data_ptr() % 16 == 0)
 
@@ -771,7 +774,7 @@ def routed_experts(x, router, correction, w13, w2, ws: RoutedWorkspace, out, n_r
     E = n_real + n_identity
     n_pairs = T * top_k
     # tensor cores when both expert products fit the grouped tcgen05 GEMM (bf16, K multiples of 64, 256-row weight pairs)
-    tc = (x.dtype == torch.bfloat16 and n_real > 0 and D % 256 == 0 and ff % 128 == 0 and x.is_contiguous()
+    tc = (LAYER_LIST_TC and x.dtype == torch.bfloat16 and n_real > 0 and D % 256 == 0 and ff % 128 == 0 and x.is_contiguous()
           and w13.stride(0) == D and w2.stride(0) == ff)
     bx = moe_block_x(n_pairs, E) if tc else ws.bx
     cap = moe_capacity_rows(n_pairs, E, bx)
